@@ -1,0 +1,154 @@
+/* vinf_b200.h - C ABI of the B200 (sm_100a) quantized-matvec engine.
+ *
+ * Drop-in for the quantized matvec path of the reference's CPython type `vinf._cuda_qwen_runtime.Runtime`
+ * (engine/csrc/megakernel/qwen_runtime.cu:2602-2704): named weight tensors kept in raw GGUF block layout in
+ * device memory, named fp32 device buffers, y = W x for 1..8 (or more) activation rows, row argmax, and the
+ * fused LM-head matvec + argmax.  Each entry point names the reference method it replaces.
+ *
+ * Conventions
+ *   - Every function returns a vqm_status.  On failure vqm_last_error() gives a message; the status maps
+ *     1:1 onto the Python exception the reference raises (KeyError, ValueError, TypeError, MemoryError,
+ *     RuntimeError for CUDA errors - engine/csrc/megakernel/qwen_runtime.cu:1100-1103).
+ *   - All kernels and asynchronous copies of a runtime go to ONE stream owned by the runtime
+ *     (vqm_stream()).  It is a blocking stream, so it also orders against work that another library
+ *     in the same process puts on the legacy default stream, which is where the reference launches.
+ *   - qmv / copy / zero are asynchronous; write / read / matvec / argmax* block, like the reference.
+ *   - One host thread drives a runtime at a time (the reference holds the GIL in every method).
+ *   - Weights are always resident in device memory: there is no host staging ring.
+ */
+#ifndef VINF_B200_H
+#define VINF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct vqm_runtime vqm_runtime;
+
+typedef enum vqm_status {
+    VQM_OK = 0,
+    VQM_ERR_KEY = 1,    /* unknown tensor / buffer name            -> KeyError     */
+    VQM_ERR_VALUE = 2,  /* bad type id, shape, size, offset, ntok  -> ValueError   */
+    VQM_ERR_TYPE = 3,   /* fp16 buffer where fp32 is required      -> TypeError    */
+    VQM_ERR_MEMORY = 4, /* device allocation failed                -> MemoryError  */
+    VQM_ERR_CUDA = 5    /* any other CUDA failure, or a kernel's bounded wait expired -> RuntimeError */
+} vqm_status;
+
+/* GGUF tensor type ids accepted by vqm_upload (engine/csrc/common/qwen_quant.cuh:17-33). */
+enum {
+    VQM_F32 = 0, VQM_F16 = 1, VQM_Q8_0 = 8, VQM_Q2_K = 10, VQM_Q3_K = 11, VQM_Q4_K = 12, VQM_Q5_K = 13,
+    VQM_Q6_K = 14, VQM_IQ2_XXS = 16, VQM_IQ2_XS = 17, VQM_IQ3_XXS = 18, VQM_IQ4_NL = 20, VQM_IQ3_S = 21,
+    VQM_IQ2_S = 22, VQM_IQ4_XS = 23
+};
+
+typedef struct vqm_tensor_info_t {
+    uint64_t addr; /* device address of the raw blocks */
+    int32_t type, rows, cols;
+    int64_t row_bytes, nbytes;
+    int32_t resident; /* always 1 */
+} vqm_tensor_info_t;
+
+/* Message of the most recent failing call on this thread (never NULL). */
+const char *vqm_last_error(void);
+
+/* Runtime(iq3s_grid) - engine/csrc/megakernel/qwen_runtime.cu:1272-1297.  iq3s_grid: the 512 x 4 byte IQ3_S
+ * codebook (2048 bytes), or NULL to leave it unset.  Uses the current CUDA device. */
+int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out);
+/* tp_dealloc - qwen_runtime.cu:1299-1336: frees every tensor and buffer the runtime owns. */
+void vqm_runtime_destroy(vqm_runtime *rt);
+
+/* Codebooks of the other IQ types: "iq2xxs_grid" (2048 B), "iq2xs_grid" (4096), "iq2s_grid" (8192),
+ * "iq3xxs_grid" (1024), "iq3s_grid" (2048).  The reference compiles the first four in
+ * (engine/csrc/common/qwen_iq_tables.h) and takes IQ3_S's from the caller; here the caller supplies all. */
+int vqm_set_codebook(vqm_runtime *rt, const char *name, const void *data, size_t nbytes);
+
+/* upload(name, data, type, cols, rows[, resident, group]) - qwen_runtime.cu:1338-1409.  Synchronous copy of
+ * raw blocks; re-upload replaces; the allocation is padded by 16 bytes and rounded up to 256. */
+int vqm_upload(vqm_runtime *rt, const char *name, const void *data, size_t nbytes, int type, int cols, int rows);
+/* free(name) / has(name) / device_bytes() - qwen_runtime.cu:1411-1432 */
+int vqm_free(vqm_runtime *rt, const char *name);
+int vqm_has(vqm_runtime *rt, const char *name, int *out);
+int vqm_device_bytes(vqm_runtime *rt, size_t *out);
+/* tensor_info(name) - qwen_runtime.cu:1458-1471 */
+int vqm_tensor_info(vqm_runtime *rt, const char *name, vqm_tensor_info_t *out);
+
+/* alloc(name, n[, elem]) - qwen_runtime.cu:1616-1650: zero-filled buffer of n elements of 4 (fp32) or 2 bytes. */
+int vqm_alloc(vqm_runtime *rt, const char *name, size_t n, int elem);
+/* Registers caller-owned device memory under a buffer name (the runtime will not free it).  Lets a second
+ * runtime or a torch tensor share memory, the use the reference makes of buffer_ptr (qwen_runtime.cu:1473-1483). */
+int vqm_bind(vqm_runtime *rt, const char *name, void *device_ptr, size_t n, int elem);
+/* Same for a weight tensor that already sits in device memory (e.g. a row shard of a larger tensor). */
+int vqm_bind_tensor(vqm_runtime *rt, const char *name, const void *device_ptr, int type, int cols, int rows);
+int vqm_release(vqm_runtime *rt, const char *buffer_name);
+/* write(name, bytes[, offset]) / read(name[, n, offset]) - qwen_runtime.cu:1819-1858; offsets in elements. */
+int vqm_write(vqm_runtime *rt, const char *name, const void *data, size_t nbytes, size_t offset);
+int vqm_read(vqm_runtime *rt, const char *name, void *out, size_t n, size_t offset);
+/* copy(dst, dst_off, src, src_off, n) - qwen_runtime.cu:2200-2217; zero(name) - :1652-1667; zero_range - :2589-2600 */
+int vqm_copy(vqm_runtime *rt, const char *dst, size_t dst_off, const char *src, size_t src_off, size_t n);
+int vqm_zero(vqm_runtime *rt, const char *name);
+int vqm_zero_range(vqm_runtime *rt, const char *name, size_t offset, size_t n);
+/* buffer_ptr(name) -> (addr, n) - qwen_runtime.cu:1473-1483; buffer_elem(name) - :2317-2322 */
+int vqm_buffer_ptr(vqm_runtime *rt, const char *name, uint64_t *addr, size_t *n);
+int vqm_buffer_elem(vqm_runtime *rt, const char *name, int *elem);
+/* Element count of a buffer of either precision (what read(name) with n = -1 returns). */
+int vqm_buffer_len(vqm_runtime *rt, const char *name, size_t *n);
+int vqm_buffer_bytes(vqm_runtime *rt, size_t *out);
+
+/* qmv(weight, x, y[, ntok]) - qwen_runtime.cu:1861-1912: y[t][r] = sum_k W[r][k] x[t][k], x = [ntok][cols],
+ * y = [ntok][rows], both fp32 buffers.  Asynchronous.  More than 8 rows run as groups of 8. */
+int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok);
+/* matvec(name, x) -> y - qwen_runtime.cu:2281-2315: synchronous single-row entry with host vectors. */
+int vqm_matvec(vqm_runtime *rt, const char *weight, const float *x_host, size_t x_bytes, float *y_host, size_t y_bytes);
+/* argmax(x, n) / argmax_rows(x, n, ntok) - qwen_runtime.cu:2167-2197: blocking; ties to the lowest index;
+ * 1 <= ntok <= 256. */
+int vqm_argmax(vqm_runtime *rt, const char *x, int n, int *out);
+int vqm_argmax_rows(vqm_runtime *rt, const char *x, int n, int ntok, int *out);
+/* The LM head in one launch: qmv(weight, x, y, ntok) followed by argmax_rows(y, rows, ntok)
+ * (engine/src/vinf/qwen_gpu.py:1068-1086; the reference fuses the two only in its megakernel,
+ * engine/csrc/megakernel/qwen_megakernel.cu:231-236,800-829).  y may be NULL to skip storing the logits.
+ * ntok <= 8.  out_ids (host, ntok ints) may be NULL: then the call is asynchronous and the ids stay in
+ * the device buffer returned by vqm_argmax_result(). */
+int vqm_qmv_argmax(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int *out_ids);
+/* Device arrays holding the last fused argmax: ids[8] (int32) and values[8] (fp32). */
+int vqm_argmax_result(vqm_runtime *rt, uint64_t *ids_addr, uint64_t *values_addr);
+/* Row offset added to the ids of the fused argmax (for a runtime that holds rows [base, base + rows) of a
+ * row-sharded LM head). */
+int vqm_set_argmax_row_base(vqm_runtime *rt, const char *weight, int row_base);
+
+/* Exact fp32 values of a weight tensor into an fp32 buffer of rows * cols elements.  No reference method;
+ * exposes the block decoders the matvec uses so that they can be checked bit for bit against the
+ * reference dequantiser (engine/src/vinf/gguf/dequant.py:17-57). */
+int vqm_dequantize(vqm_runtime *rt, const char *weight, const char *out);
+
+/* set_gemm_min_rows(n) - qwen_runtime.cu:2324-2330.  Accepted for compatibility (n >= 0). */
+int vqm_set_gemm_min_rows(vqm_runtime *rt, int n);
+/* synchronize() / mem_info() - qwen_runtime.cu:2267-2278.  synchronize also reports a kernel whose
+ * bounded wait expired as VQM_ERR_CUDA. */
+int vqm_synchronize(vqm_runtime *rt);
+int vqm_mem_info(size_t *free_bytes, size_t *total_bytes);
+
+/* The runtime's stream (a cudaStream_t), so that a caller can record events on it or order other work. */
+void *vqm_stream(vqm_runtime *rt);
+/* Records the launches made between begin and end into a CUDA graph instead of running them (a whole
+ * decoder pass of qmv calls becomes one launch).  Blocking entry points are not allowed in between. */
+int vqm_capture_begin(vqm_runtime *rt);
+int vqm_capture_end(vqm_runtime *rt, int *graph_id);
+int vqm_graph_launch(vqm_runtime *rt, int graph_id);
+int vqm_graph_destroy(vqm_runtime *rt, int graph_id);
+/* Number of kernels this runtime has launched (graph launches count their kernels). */
+int vqm_launch_count(vqm_runtime *rt, uint64_t *out);
+
+/* Stateless entry point for callers that own all memory: y = W x on `stream` (a cudaStream_t, NULL = legacy
+ * default).  w: raw blocks, 16-byte aligned and readable 16 bytes past the end; x: [ntok][cols], y:
+ * [ntok][rows], 16-byte aligned fp32; codebook: device copy of the type's codebook or NULL; status: device
+ * word that receives a non-zero code if a bounded wait expires (may not be NULL).  1 <= ntok <= 8. */
+int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
+                unsigned *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VINF_B200_H */

@@ -1,0 +1,331 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle on the same seeded inputs.
+
+Bars: dequantised values bit-exact; matvec relative L2 error <= 1e-5 against dequantise + fp64 matvec (and
+the reference's own per-element bound 1e-4 * max|ref| + 1e-5, engine/tests/test_phase30_cuda_qmatvec.py:67-72);
+argmax ids exact.  Shapes follow the reference's tests (5 x 512 for every type, 70 x 512 with 37 rows of
+activations, engine/tests/test_phase31i_prefill.py:194-219) plus ragged and benchmark-sized ones.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import dequant_np as O
+from tests import oracle_libs
+from vinf_3080ti_b200.gguf_types import TRAITS, GGUFTensorType as T
+from vinf_3080ti_b200.synth import synthetic_activations, synthetic_blocks
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+ALL_TYPES = sorted(TRAITS)
+REL_L2 = 1e-5  # fp32 accumulation, stated by the task
+
+
+@pytest.fixture(scope="module")
+def rt(codebooks):
+    from vinf_3080ti_b200.runtime import Runtime
+
+    runtime = Runtime(codebooks["iq3s_grid"], codebooks)
+    yield runtime
+    runtime.close()
+
+
+@pytest.fixture(scope="module")
+def clib():
+    return oracle_libs.load_c_oracle()
+
+
+def rel_l2(got: np.ndarray, ref: np.ndarray) -> float:
+    return float(np.linalg.norm(got.astype(np.float64) - ref) / max(np.linalg.norm(ref), 1e-300))
+
+
+def run_qmv(rt, raw: np.ndarray, t: T, rows: int, cols: int, x: np.ndarray, name: str = "w") -> np.ndarray:
+    ntok = x.shape[0]
+    rt.upload(name, raw, int(t), cols, rows)
+    rt.alloc("x", ntok * cols)
+    rt.alloc("y", ntok * rows)
+    rt.write("x", np.ascontiguousarray(x, dtype=np.float32))
+    rt.qmv(name, "x", "y", ntok)
+    rt.synchronize()
+    return rt.read_array("y").reshape(ntok, rows).copy()
+
+
+# ---- dequantised values: bit-exact ------------------------------------------------------------------
+
+@pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
+def test_dequantised_values_equal_the_reference_dequantiser(rt, t):
+    with np.load(GOLDEN / "dequant_golden.npz") as z:
+        rows, cols = (int(v) for v in z["shape"])
+        raw, want = z[f"raw_{int(t)}"], z[f"val_{int(t)}"]
+    rt.upload("w", raw, int(t), cols, rows)
+    rt.alloc("deq", rows * cols)
+    rt.dequantize("w", "deq")
+    rt.synchronize()
+    got = rt.read_array("deq")
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
+def test_dequantised_values_bit_exact_on_benchmark_width_rows(rt, codebooks, t):
+    rng = np.random.default_rng(500 + int(t))
+    rows, cols = 64, 5120
+    raw = synthetic_blocks(t, rows, cols, rng)
+    want = O.dequantize(raw, int(t), rows * cols, codebooks).astype(np.float32)
+    rt.upload("w", raw, int(t), cols, rows)
+    rt.alloc("deq", rows * cols)
+    rt.dequantize("w", "deq")
+    rt.synchronize()
+    assert np.array_equal(rt.read_array("deq").view(np.uint32), want.view(np.uint32))
+
+
+# ---- matvec ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
+def test_matvec_entry_on_the_reference_test_shape(rt, codebooks, t):
+    """5 x 512, one activation row, through the synchronous matvec entry (test_phase30_cuda_qmatvec.py:74-86)."""
+    rng = np.random.default_rng(30 + int(t))
+    rows, cols = 5, 512
+    raw = synthetic_blocks(t, rows, cols, rng, 0.001, 0.05)
+    x = rng.uniform(-1, 1, cols).astype(np.float32)
+    rt.upload("w", raw, int(t), cols, rows)
+    got = np.frombuffer(rt.matvec("w", x), dtype=np.float32)
+    ref = O.matvec(raw, int(t), rows, cols, x, codebooks)
+    assert np.all(np.isfinite(got))
+    assert np.all(np.abs(got - ref) <= 1e-4 * max(1e-6, np.abs(ref).max()) + 1e-5)
+    assert rel_l2(got, ref) <= REL_L2
+    rt.free("w")
+    assert rt.device_bytes() == 0
+
+
+@pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
+@pytest.mark.parametrize("ntok", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_qmv_every_type_and_row_count(rt, codebooks, t, ntok):
+    rng = np.random.default_rng(1000 + 16 * int(t) + ntok)
+    rows, cols = 70, 1536  # rows not a multiple of the row-group height; one full and one half segment
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    got = run_qmv(rt, raw, t, rows, cols, x)
+    ref = O.matvec(raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, ref) <= REL_L2
+
+
+@pytest.mark.parametrize("t,rows,cols", [
+    (T.Q8_0, 3, 32), (T.IQ4_NL, 1, 32), (T.F32, 9, 32), (T.F16, 2, 64), (T.Q4_K, 1, 256), (T.Q6_K, 7, 256),
+    (T.Q3_K, 1025, 768), (T.IQ2_XXS, 33, 2304), (T.Q5_K, 300, 1024), (T.Q2_K, 5, 4352), (T.IQ4_XS, 129, 5120),
+], ids=lambda v: getattr(v, "name", str(v)))
+def test_qmv_ragged_and_minimal_shapes(rt, codebooks, t, rows, cols):
+    rng = np.random.default_rng(rows * 7919 + cols)
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(3, cols, rng)
+    got = run_qmv(rt, raw, t, rows, cols, x)
+    ref = O.matvec(raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, ref) <= REL_L2
+
+
+@pytest.mark.parametrize("t", [T.Q4_K, T.Q6_K, T.Q3_K, T.IQ4_XS, T.IQ2_S, T.Q8_0], ids=lambda t: t.name)
+def test_batched_pass_equals_single_row_passes_bit_for_bit(rt, t):
+    """engine/tests/test_phase31c_batched_forward.py:53-66 at the matvec level."""
+    rng = np.random.default_rng(31 + int(t))
+    rows, cols, ntok = 300, 2048, 8
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    together = run_qmv(rt, raw, t, rows, cols, x)
+    for k in range(ntok):
+        alone = run_qmv(rt, raw, t, rows, cols, x[k : k + 1])
+        assert np.array_equal(alone[0].view(np.uint32), together[k].view(np.uint32))
+
+
+@pytest.mark.parametrize("t", [T.Q4_K, T.Q6_K], ids=lambda t: t.name)
+def test_wide_pass_runs_as_groups_of_eight(rt, codebooks, t):
+    """70 x 512 weights, 37 activation rows: partial last group (test_phase31i_prefill.py:194-219)."""
+    rng = np.random.default_rng(37)
+    rows, cols, ntok = 70, 512, 37
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    got = run_qmv(rt, raw, t, rows, cols, x)
+    ref = O.matvec(raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, ref) <= REL_L2
+
+
+@pytest.mark.parametrize("t,rows,cols,ntok", [
+    (T.Q4_K, 17408, 5120, 1), (T.Q4_K, 17408, 5120, 8), (T.Q4_K, 5120, 17408, 4), (T.Q3_K, 17408, 5120, 4),
+    (T.Q6_K, 6144, 5120, 2), (T.Q6_K, 1024, 5120, 1), (T.Q6_K, 5120, 6144, 8), (T.IQ4_XS, 17408, 5120, 1),
+    (T.IQ2_XXS, 17408, 5120, 8), (T.IQ2_S, 17408, 5120, 1), (T.IQ3_S, 17408, 5120, 8), (T.IQ4_NL, 5120, 17408, 1),
+], ids=lambda v: getattr(v, "name", str(v)))
+def test_qmv_benchmark_shapes(rt, clib, codebooks, t, rows, cols, ntok):
+    rng = np.random.default_rng(0)
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    got = run_qmv(rt, raw, t, rows, cols, x)
+    ref = oracle_libs.c_qmv(clib, raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, ref) <= REL_L2
+
+
+def test_linearity_at_full_size(rt):
+    """Size-independent property: W(a*x1 + x2) = a*W x1 + W x2 up to fp32 rounding, no oracle needed."""
+    rng = np.random.default_rng(5)
+    rows, cols = 17408, 5120
+    raw = synthetic_blocks(T.Q4_K, rows, cols, rng)
+    x = synthetic_activations(2, cols, rng)
+    combo = (2.0 * x[0] + x[1])[None, :]
+    y = run_qmv(rt, raw, T.Q4_K, rows, cols, np.concatenate([x, combo]))
+    ref = 2.0 * y[0].astype(np.float64) + y[1]
+    assert rel_l2(y[2], ref) <= 1e-5
+
+
+# ---- argmax --------------------------------------------------------------------------------------------
+
+def test_argmax_rows_rules(rt):
+    n, ntok = 1000, 5
+    rng = np.random.default_rng(9)
+    y = rng.standard_normal((ntok, n)).astype(np.float32)
+    y[1, 17] = y[1, 900] = 50.0  # tie -> lowest index
+    y[2, :] = -np.inf  # nothing above -inf -> 0x7fffffff
+    y[3, :] = np.nan
+    y[3, 5] = -3.0
+    y[4, 999] = 99.0
+    rt.alloc("logits", ntok * n)
+    rt.write("logits", y)
+    assert rt.argmax_rows("logits", n, ntok) == [int(v) for v in O.argmax_rows(y)]
+    assert rt.argmax_rows("logits", n, ntok)[1:4] == [17, 0x7FFFFFFF, 5]
+    assert rt.argmax("logits", n) == int(np.argmax(y[0]))
+    with pytest.raises(ValueError):
+        rt.argmax_rows("logits", n, 257)
+
+
+@pytest.mark.parametrize("t,ntok", [(T.Q6_K, 1), (T.Q6_K, 4), (T.Q4_K, 8), (T.IQ4_XS, 3)], ids=lambda v: getattr(v, "name", str(v)))
+def test_fused_lm_head_argmax_matches_unfused_and_oracle(rt, codebooks, t, ntok):
+    rng = np.random.default_rng(77 + ntok)
+    rows, cols = 4099, 1024
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    ref = O.matvec(raw, int(t), rows, cols, x, codebooks)
+    top2 = np.sort(ref, axis=1)[:, -2:]
+    assert np.all(top2[:, 1] - top2[:, 0] > 1e-4 * np.abs(top2[:, 1])), "near-tie in the synthetic logits: reseed"
+    logits = run_qmv(rt, raw, t, rows, cols, x)
+    unfused = rt.argmax_rows("y", rows, ntok)
+    rt.alloc("y2", ntok * rows)
+    fused = rt.qmv_argmax("w", "x", "y2", ntok)
+    assert fused == unfused == [int(v) for v in O.argmax_rows(ref)]
+    assert np.array_equal(rt.read_array("y2").view(np.uint32), logits.reshape(-1).view(np.uint32))
+    assert rt.qmv_argmax("w", "x", None, ntok) == fused  # without storing the logits
+    rt.qmv_argmax("w", "x", None, ntok, blocking=False)  # ids stay on the device; twice in a row works
+    assert rt.qmv_argmax("w", "x", None, ntok) == fused
+
+
+def test_fused_argmax_ties_go_to_the_lowest_row(rt):
+    rows, cols = 515, 256
+    w = np.zeros((rows, cols), dtype=np.float32)
+    w[[7, 300, 514], 0] = 2.0  # three equal maxima
+    w[100, 0] = -1.0
+    x = np.zeros((2, cols), dtype=np.float32)
+    x[0, 0] = 1.0
+    x[1, 0] = -1.0  # second row: maximum is row 100's +1
+    rt.upload("w", w, int(T.F32), cols, rows)
+    rt.alloc("x", 2 * cols)
+    rt.write("x", x)
+    assert rt.qmv_argmax("w", "x", None, 2) == [7, 100]
+
+
+# ---- boundary behaviour --------------------------------------------------------------------------------
+
+def test_error_contract(rt):
+    """engine/tests/test_phase30_cuda_qmatvec.py:127-134 and the checks of Runtime_qmv / find_buffer."""
+    with pytest.raises(ValueError):
+        rt.upload("w", bytes(34), 2, 32, 1)  # Q4_0: no kernel
+    with pytest.raises(ValueError):
+        rt.upload("w", bytes(33), int(T.Q8_0), 32, 1)  # wrong byte count
+    with pytest.raises(ValueError):
+        rt.upload("w", bytes(144), int(T.Q4_K), 100, 1)  # cols not a multiple of the block
+    with pytest.raises(KeyError):
+        rt.matvec("missing", np.zeros(32, dtype=np.float32))
+    with pytest.raises(KeyError):
+        rt.free("missing")
+    rt.upload("w8", bytes(34 * 2), int(T.Q8_0), 32, 2)
+    rt.alloc("x", 32)
+    rt.alloc("y", 2)
+    with pytest.raises(KeyError):
+        rt.qmv("nope", "x", "y")
+    with pytest.raises(KeyError):
+        rt.qmv("w8", "nope", "y")
+    with pytest.raises(ValueError):
+        rt.qmv("w8", "x", "y", 0)
+    with pytest.raises(ValueError):
+        rt.qmv("w8", "x", "y", 2)  # buffers too small for two rows
+    rt.alloc("h", 64, 2)
+    with pytest.raises(TypeError):
+        rt.qmv("w8", "h", "y")
+    with pytest.raises(ValueError):
+        rt.alloc("bad", 0)
+    with pytest.raises(ValueError):
+        rt.alloc("bad", 4, 3)
+    with pytest.raises(ValueError):
+        rt.write("x", bytes(4 * 33))
+    with pytest.raises(ValueError):
+        rt.read("x", 33)
+    assert rt.has("w8") and not rt.has("nope")
+    addr, typ, rows, cols, row_bytes, nbytes, resident = rt.tensor_info("w8")
+    assert (typ, rows, cols, row_bytes, nbytes, resident) == (8, 2, 32, 34, 68, True) and addr % 256 == 0
+
+
+def test_buffers_copy_zero_and_reupload(rt):
+    rt.alloc("a", 16)
+    rt.alloc("b", 16)
+    rt.write("a", np.arange(16, dtype=np.float32))
+    rt.copy("b", 4, "a", 8, 4)
+    rt.synchronize()
+    assert list(rt.read_array("b")[4:8]) == [8.0, 9.0, 10.0, 11.0] and rt.read_array("b")[0] == 0.0
+    rt.zero_range("a", 2, 3)
+    rt.synchronize()
+    assert list(rt.read_array("a")[:6]) == [0.0, 1.0, 0.0, 0.0, 0.0, 5.0]
+    rt.zero("a")
+    assert not rt.read_array("a").any()
+    assert rt.read("a", 2, 14) == bytes(8)
+    rt.alloc("a", 4)  # re-alloc replaces
+    assert rt.buffer_ptr("a")[1] == 4
+
+
+def test_codebook_must_be_set_before_use():
+    from vinf_3080ti_b200.runtime import Runtime
+
+    bare = Runtime()
+    rng = np.random.default_rng(1)
+    bare.upload("w", synthetic_blocks(T.IQ2_XS, 2, 256, rng), int(T.IQ2_XS), 256, 2)
+    bare.alloc("x", 256)
+    bare.alloc("y", 2)
+    with pytest.raises(ValueError, match="codebook"):
+        bare.qmv("w", "x", "y")
+    bare.close()
+
+
+def test_a_captured_pass_replays_as_one_graph(rt, codebooks):
+    rng = np.random.default_rng(12)
+    shapes = [(T.Q6_K, 96, 512), (T.Q3_K, 200, 512), (T.Q4_K, 512, 768)]
+    raws = [synthetic_blocks(t, r, c, rng) for t, r, c in shapes]
+    for i, ((t, r, c), raw) in enumerate(zip(shapes, raws)):
+        rt.upload(f"g{i}", raw, int(t), c, r)
+        rt.alloc(f"gy{i}", 2 * r)
+    x = synthetic_activations(2, 512, rng)
+    x3 = synthetic_activations(2, 768, rng)
+    rt.alloc("gx", 2 * 512)
+    rt.alloc("gx3", 2 * 768)
+    rt.write("gx", x)
+    rt.write("gx3", x3)
+    before = rt.launch_count()
+    rt.capture_begin()
+    rt.qmv("g0", "gx", "gy0", 2)
+    rt.qmv("g1", "gx", "gy1", 2)
+    rt.qmv("g2", "gx3", "gy2", 2)
+    with pytest.raises(ValueError):
+        rt.read("gy0")  # blocking calls are refused during capture
+    graph = rt.capture_end()
+    assert rt.launch_count() == before  # nothing ran yet
+    rt.graph_launch(graph)
+    rt.synchronize()
+    assert rt.launch_count() == before + 3
+    for i, ((t, r, c), raw) in enumerate(zip(shapes, raws)):
+        ref = O.matvec(raw, int(t), r, c, x3 if c == 768 else x, codebooks)
+        assert rel_l2(rt.read_array(f"gy{i}").reshape(2, r), ref) <= REL_L2
+    rt.graph_destroy(graph)

@@ -1,0 +1,45 @@
+// Host-visible declarations shared by the kernel translation units and the runtime.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace vqm {
+
+struct MatvecArgs {
+    const uint8_t *w;        // raw blocks, 16-byte aligned, readable up to 15 bytes past the end
+    const float *x;          // [M][cols] fp32, 16-byte aligned
+    float *y;                // [M][rows] fp32 (may be null when only the argmax is wanted)
+    const uint8_t *codebook;  // device copy of the type's GGUF codebook (IQ2/IQ3 types), else null
+    unsigned *status;        // device error word (0 = fine)
+    // fused argmax (all null / 0 when unused)
+    float *part_val;         // [kMaxTok][gridDim.x]
+    int *part_idx;           // [kMaxTok][gridDim.x]
+    unsigned *done_counter;  // zero before the launch; the kernel leaves it zero
+    int *out_idx;            // [M] winning row (+ row_base), 0x7fffffff if the column has no value above -inf
+    float *out_val;          // [M] winning value (may be null)
+    int rows, cols;
+    long long row_bytes;
+    int row_base;            // added to row numbers reported by the argmax (row-sharded weights)
+};
+
+enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1 };
+
+// One launcher per GGUF type (vqm_matvec_type.cu).  m: activation rows (1..8); rw: preferred rows per warp
+// row group; sm_count: SMs of the device; grid_out (optional) receives the grid size used.
+#define VQM_FOR_EACH_TYPE(X) \
+    X(0, F32) X(1, F16) X(8, Q8_0) X(10, Q2_K) X(11, Q3_K) X(12, Q4_K) X(13, Q5_K) X(14, Q6_K) X(16, IQ2_XXS) \
+    X(17, IQ2_XS) X(18, IQ3_XXS) X(20, IQ4_NL) X(21, IQ3_S) X(22, IQ2_S) X(23, IQ4_XS)
+#define VQM_DECLARE_LAUNCHER(id, name) \
+    cudaError_t launch_qmv_##name(const MatvecArgs &a, int m, int rw, int sm_count, cudaStream_t stream, int *grid_out);
+VQM_FOR_EACH_TYPE(VQM_DECLARE_LAUNCHER)
+#undef VQM_DECLARE_LAUNCHER
+
+constexpr int kMaxGrid = 4096;  // upper bound on the matvec grid (sizes the argmax partial arrays)
+
+cudaError_t launch_argmax_rows(const float *x, int n, int ntok, int *out, cudaStream_t stream);
+cudaError_t launch_dequant(int type, const uint8_t *w, float *out, long long numel, const uint8_t *codebook,
+                           cudaStream_t stream);
+
+}  // namespace vqm

@@ -1,0 +1,746 @@
+// The runtime object behind the C ABI (include/vinf_b200.h): named weight tensors in raw GGUF block layout,
+// named device buffers, and the entry points that launch the kernels.  Mirrors the quantized-matvec part of
+// the reference's CPython type (engine/csrc/megakernel/qwen_runtime.cu:878-910 for the two records, :1198-1230
+// for the lookups and their errors, :1338-1409 upload, :1616-1650 alloc, :1819-1912 write/read/qmv,
+// :2167-2197 argmax, :2281-2315 matvec).  Weights are always resident: there is no host ring or VMM group.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/vinf_b200.h"
+#include "vqm_formats.cuh"
+#include "vqm_kernels.h"
+
+namespace {
+
+thread_local std::string g_error = "";
+
+int fail(int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_error = buf;
+    return status;
+}
+
+int cuda_fail(const char *ctx, cudaError_t err) {
+    // "<context> failed: <cudaGetErrorString>", the reference's message (qwen_runtime.cu:1100-1103)
+    return fail(err == cudaErrorMemoryAllocation ? VQM_ERR_MEMORY : VQM_ERR_CUDA, "%s failed: %s", ctx, cudaGetErrorString(err));
+}
+
+struct Tensor {
+    uint8_t *data = nullptr;
+    int type = 0, rows = 0, cols = 0;
+    size_t row_bytes = 0, nbytes = 0;
+    int argmax_row_base = 0;
+    bool owned = true;
+};
+
+struct Buffer {
+    void *data = nullptr;
+    size_t n = 0;
+    int elem = 4;
+    bool owned = true;
+    size_t bytes() const { return n * static_cast<size_t>(elem); }
+};
+
+struct Graph {
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;
+};
+
+const char *const kCodebookNames[5] = {"iq2xxs_grid", "iq2xs_grid", "iq2s_grid", "iq3xxs_grid", "iq3s_grid"};
+const int kCodebookTypes[5] = {vqm::kIQ2_XXS, vqm::kIQ2_XS, vqm::kIQ2_S, vqm::kIQ3_XXS, vqm::kIQ3_S};
+
+}  // namespace
+
+struct vqm_runtime {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    std::unordered_map<std::string, Tensor> tensors;
+    std::unordered_map<std::string, Buffer> buffers;
+    uint8_t *codebooks[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    // fixed device scratch: status word, argmax partials/results
+    unsigned *status = nullptr;
+    unsigned *done_counter = nullptr;
+    float *part_val = nullptr;
+    int *part_idx = nullptr;
+    int *argmax_ids = nullptr;     // [256]: fused argmax uses the first 8, argmax_rows up to 256
+    float *argmax_vals = nullptr;  // [8]
+    // scratch of the synchronous matvec entry
+    float *scratch_x = nullptr, *scratch_y = nullptr;
+    size_t scratch_x_n = 0, scratch_y_n = 0;
+    int gemm_min_rows = 0;
+    bool capturing = false;
+    uint64_t launches = 0, capture_launches = 0;
+    std::vector<Graph> graphs;
+};
+
+namespace {
+
+const uint8_t *codebook_for(vqm_runtime *rt, int type) {
+    for (int i = 0; i < 5; ++i)
+        if (kCodebookTypes[i] == type) return rt->codebooks[i];
+    return nullptr;
+}
+
+Tensor *find_tensor(vqm_runtime *rt, const char *name, int *status) {
+    auto it = rt->tensors.find(name);
+    if (it == rt->tensors.end()) {
+        *status = fail(VQM_ERR_KEY, "weight tensor %s is not loaded", name);
+        return nullptr;
+    }
+    return &it->second;
+}
+
+Buffer *find_any_buffer(vqm_runtime *rt, const char *name, int *status) {
+    auto it = rt->buffers.find(name);
+    if (it == rt->buffers.end()) {
+        *status = fail(VQM_ERR_KEY, "device buffer %s is not allocated", name);
+        return nullptr;
+    }
+    return &it->second;
+}
+
+// fp32 buffer with at least min_n elements (qwen_runtime.cu:1207-1222)
+float *find_f32(vqm_runtime *rt, const char *name, size_t min_n, int *status) {
+    Buffer *b = find_any_buffer(rt, name, status);
+    if (b == nullptr) return nullptr;
+    if (b->elem != 4) {
+        *status = fail(VQM_ERR_TYPE, "device buffer %s is fp16 (KV cache), not fp32", name);
+        return nullptr;
+    }
+    if (b->n < min_n) {
+        *status = fail(VQM_ERR_VALUE, "device buffer %s has %zu floats, need %zu", name, b->n, min_n);
+        return nullptr;
+    }
+    return static_cast<float *>(b->data);
+}
+
+void release(Tensor &t) {
+    if (t.owned && t.data != nullptr) cudaFree(t.data);
+    t.data = nullptr;
+}
+void release(Buffer &b) {
+    if (b.owned && b.data != nullptr) cudaFree(b.data);
+    b.data = nullptr;
+}
+
+int no_capture(vqm_runtime *rt, const char *what) {
+    if (rt->capturing) return fail(VQM_ERR_VALUE, "%s is not allowed while a graph is being captured", what);
+    return VQM_OK;
+}
+
+void count_launch(vqm_runtime *rt, uint64_t n = 1) {
+    if (rt->capturing) rt->capture_launches += n;
+    else rt->launches += n;
+}
+
+cudaError_t dispatch_qmv(int type, const vqm::MatvecArgs &a, int m, int rw, int sm_count, cudaStream_t stream, int *grid) {
+    switch (type) {
+#define VQM_CASE(id, name) \
+    case id: return vqm::launch_qmv_##name(a, m, rw, sm_count, stream, grid);
+        VQM_FOR_EACH_TYPE(VQM_CASE)
+#undef VQM_CASE
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// Rows per warp row group: 4 when that still gives every warp of a full grid some work, else 2.
+int pick_rw(int rows, int sm_count) { return rows / 4 >= sm_count * 8 ? 4 : 2; }
+
+int check_shape(const char *name, int type, int cols, int rows, size_t *row_bytes) {
+    const vqm::Traits t = vqm::traits_of(type);
+    if (t.block == 0) return fail(VQM_ERR_VALUE, "unsupported GGUF tensor type id %d for CUDA matvec", type);
+    if (cols <= 0 || rows <= 0 || cols % t.block != 0)
+        return fail(VQM_ERR_VALUE, "%s: cols=%d must be a positive multiple of the block size", name, cols);
+    *row_bytes = static_cast<size_t>(cols / t.block) * t.size;
+    return VQM_OK;
+}
+
+// Launches y = W x for m <= 8 rows of x, optionally with the fused argmax.
+int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int m, bool with_argmax) {
+    const uint8_t *cb = codebook_for(rt, t.type);
+    if (vqm::grid_is_codebook(t.type) && cb == nullptr)
+        return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t.type);
+    vqm::MatvecArgs a{};
+    a.w = t.data;
+    a.x = x;
+    a.y = y;
+    a.codebook = cb;
+    a.status = rt->status;
+    a.rows = t.rows;
+    a.cols = t.cols;
+    a.row_bytes = static_cast<long long>(t.row_bytes);
+    if (with_argmax) {
+        a.part_val = rt->part_val;
+        a.part_idx = rt->part_idx;
+        a.done_counter = rt->done_counter;
+        a.out_idx = rt->argmax_ids;
+        a.out_val = rt->argmax_vals;
+        a.row_base = t.argmax_row_base;
+    }
+    const cudaError_t err = dispatch_qmv(t.type, a, m, pick_rw(t.rows, rt->sm_count), rt->sm_count, rt->stream, nullptr);
+    if (err != cudaSuccess) return cuda_fail("qmv launch", err);
+    count_launch(rt);
+    return VQM_OK;
+}
+
+int check_status_word(vqm_runtime *rt, const char *ctx) {
+    unsigned host = 0;
+    cudaError_t err = cudaMemcpyAsync(&host, rt->status, sizeof(host), cudaMemcpyDeviceToHost, rt->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+    if (err != cudaSuccess) return cuda_fail(ctx, err);
+    if (host != 0) {
+        cudaMemsetAsync(rt->status, 0, sizeof(unsigned), rt->stream);
+        return fail(VQM_ERR_CUDA, "%s failed: a kernel gave up waiting for its weight copies (status %u)", ctx, host);
+    }
+    return VQM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *vqm_last_error(void) { return g_error.c_str(); }
+
+int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) {
+    if (out == nullptr) return fail(VQM_ERR_VALUE, "out must not be NULL");
+    *out = nullptr;
+    if (iq3s_grid != nullptr && nbytes != 2048)
+        return fail(VQM_ERR_VALUE, "iq3s_grid must be 2048 bytes (512 entries x 4 values)");
+    vqm_runtime *rt = new vqm_runtime();
+    cudaError_t err = cudaGetDevice(&rt->device);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&rt->sm_count, cudaDevAttrMultiProcessorCount, rt->device);
+    if (err == cudaSuccess) err = cudaStreamCreate(&rt->stream);
+    if (err == cudaSuccess) err = cudaMalloc(&rt->status, 256);
+    if (err == cudaSuccess) err = cudaMemset(rt->status, 0, 256);
+    if (err == cudaSuccess) err = cudaMalloc(&rt->part_val, sizeof(float) * 8 * vqm::kMaxGrid);
+    if (err == cudaSuccess) err = cudaMalloc(&rt->part_idx, sizeof(int) * 8 * vqm::kMaxGrid);
+    if (err == cudaSuccess) err = cudaMalloc(&rt->argmax_ids, sizeof(int) * 256);
+    if (err == cudaSuccess) err = cudaMalloc(&rt->argmax_vals, sizeof(float) * 8);
+    if (err != cudaSuccess) {
+        const int rc = cuda_fail("runtime setup", err);
+        vqm_runtime_destroy(rt);
+        return rc;
+    }
+    rt->done_counter = rt->status + 16;
+    if (iq3s_grid != nullptr) {
+        const int rc = vqm_set_codebook(rt, "iq3s_grid", iq3s_grid, nbytes);
+        if (rc != VQM_OK) {
+            vqm_runtime_destroy(rt);
+            return rc;
+        }
+    }
+    *out = rt;
+    return VQM_OK;
+}
+
+void vqm_runtime_destroy(vqm_runtime *rt) {
+    if (rt == nullptr) return;
+    if (rt->stream != nullptr) cudaStreamSynchronize(rt->stream);
+    for (auto &g : rt->graphs)
+        if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
+    for (auto &kv : rt->tensors) release(kv.second);
+    for (auto &kv : rt->buffers) release(kv.second);
+    for (auto &cb : rt->codebooks) cudaFree(cb);
+    cudaFree(rt->status);
+    cudaFree(rt->part_val);
+    cudaFree(rt->part_idx);
+    cudaFree(rt->argmax_ids);
+    cudaFree(rt->argmax_vals);
+    cudaFree(rt->scratch_x);
+    cudaFree(rt->scratch_y);
+    if (rt->stream != nullptr) cudaStreamDestroy(rt->stream);
+    delete rt;
+}
+
+int vqm_set_codebook(vqm_runtime *rt, const char *name, const void *data, size_t nbytes) {
+    for (int i = 0; i < 5; ++i) {
+        if (strcmp(name, kCodebookNames[i]) != 0) continue;
+        const size_t want = static_cast<size_t>(vqm::grid_bytes(kCodebookTypes[i]));
+        if (data == nullptr || nbytes != want) return fail(VQM_ERR_VALUE, "%s must be %zu bytes", name, want);
+        cudaError_t err = cudaSuccess;
+        if (rt->codebooks[i] == nullptr) err = cudaMalloc(&rt->codebooks[i], want);
+        if (err == cudaSuccess) err = cudaMemcpy(rt->codebooks[i], data, want, cudaMemcpyHostToDevice);
+        if (err != cudaSuccess) return cuda_fail("codebook upload", err);
+        return VQM_OK;
+    }
+    return fail(VQM_ERR_KEY, "unknown codebook %s", name);
+}
+
+int vqm_upload(vqm_runtime *rt, const char *name, const void *data, size_t nbytes, int type, int cols, int rows) {
+    size_t row_bytes = 0;
+    int rc = check_shape(name, type, cols, rows, &row_bytes);
+    if (rc != VQM_OK) return rc;
+    const size_t want = row_bytes * static_cast<size_t>(rows);
+    if (nbytes != want) return fail(VQM_ERR_VALUE, "%s: got %zu bytes, expected %zu", name, nbytes, want);
+    if ((rc = no_capture(rt, "upload")) != VQM_OK) return rc;
+    auto it = rt->tensors.find(name);
+    if (it != rt->tensors.end()) {
+        cudaStreamSynchronize(rt->stream);
+        release(it->second);
+        rt->tensors.erase(it);
+    }
+    Tensor t;
+    // +16: bulk copies are widened to 16-byte boundaries and may read up to 15 bytes past the end
+    const size_t padded = (want + 16 + 255) / 256 * 256;
+    cudaError_t err = cudaMalloc(&t.data, padded);
+    if (err == cudaSuccess) err = cudaMemset(t.data + want, 0, padded - want);
+    if (err == cudaSuccess) err = cudaMemcpy(t.data, data, want, cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) {
+        release(t);
+        return cuda_fail("upload tensor", err);
+    }
+    t.type = type;
+    t.rows = rows;
+    t.cols = cols;
+    t.row_bytes = row_bytes;
+    t.nbytes = want;
+    rt->tensors[name] = t;
+    return VQM_OK;
+}
+
+int vqm_bind_tensor(vqm_runtime *rt, const char *name, const void *device_ptr, int type, int cols, int rows) {
+    size_t row_bytes = 0;
+    const int rc = check_shape(name, type, cols, rows, &row_bytes);
+    if (rc != VQM_OK) return rc;
+    if (device_ptr == nullptr || (reinterpret_cast<uintptr_t>(device_ptr) & 15u) != 0)
+        return fail(VQM_ERR_VALUE, "%s: device pointer must be 16-byte aligned", name);
+    auto it = rt->tensors.find(name);
+    if (it != rt->tensors.end()) {
+        cudaStreamSynchronize(rt->stream);
+        release(it->second);
+        rt->tensors.erase(it);
+    }
+    Tensor t;
+    t.data = const_cast<uint8_t *>(static_cast<const uint8_t *>(device_ptr));
+    t.owned = false;
+    t.type = type;
+    t.rows = rows;
+    t.cols = cols;
+    t.row_bytes = row_bytes;
+    t.nbytes = row_bytes * static_cast<size_t>(rows);
+    rt->tensors[name] = t;
+    return VQM_OK;
+}
+
+int vqm_free(vqm_runtime *rt, const char *name) {
+    auto it = rt->tensors.find(name);
+    if (it == rt->tensors.end()) return fail(VQM_ERR_KEY, "%s", name);
+    cudaStreamSynchronize(rt->stream);
+    release(it->second);
+    rt->tensors.erase(it);
+    return VQM_OK;
+}
+
+int vqm_has(vqm_runtime *rt, const char *name, int *out) {
+    *out = rt->tensors.count(name) != 0;
+    return VQM_OK;
+}
+
+int vqm_device_bytes(vqm_runtime *rt, size_t *out) {
+    size_t total = 0;
+    for (auto &kv : rt->tensors) total += kv.second.nbytes;
+    *out = total;
+    return VQM_OK;
+}
+
+int vqm_tensor_info(vqm_runtime *rt, const char *name, vqm_tensor_info_t *out) {
+    int rc = VQM_OK;
+    Tensor *t = find_tensor(rt, name, &rc);
+    if (t == nullptr) return rc;
+    out->addr = reinterpret_cast<uintptr_t>(t->data);
+    out->type = t->type;
+    out->rows = t->rows;
+    out->cols = t->cols;
+    out->row_bytes = static_cast<int64_t>(t->row_bytes);
+    out->nbytes = static_cast<int64_t>(t->nbytes);
+    out->resident = 1;
+    return VQM_OK;
+}
+
+int vqm_alloc(vqm_runtime *rt, const char *name, size_t n, int elem) {
+    if (n == 0 || n > (static_cast<size_t>(1) << 62)) return fail(VQM_ERR_VALUE, "buffer %s size must be positive", name);
+    if (elem != 4 && elem != 2) return fail(VQM_ERR_VALUE, "element size must be 4 (fp32) or 2 (fp16)");
+    const int rc = no_capture(rt, "alloc");
+    if (rc != VQM_OK) return rc;
+    auto it = rt->buffers.find(name);
+    if (it != rt->buffers.end()) {
+        cudaStreamSynchronize(rt->stream);
+        release(it->second);
+        rt->buffers.erase(it);
+    }
+    Buffer b;
+    b.elem = elem;
+    b.n = n;
+    cudaError_t err = cudaMalloc(&b.data, b.bytes());
+    if (err == cudaSuccess) err = cudaMemset(b.data, 0, b.bytes());
+    if (err != cudaSuccess) {
+        release(b);
+        return cuda_fail("cudaMalloc buffer", err);
+    }
+    rt->buffers[name] = b;
+    return VQM_OK;
+}
+
+int vqm_bind(vqm_runtime *rt, const char *name, void *device_ptr, size_t n, int elem) {
+    if (n == 0) return fail(VQM_ERR_VALUE, "buffer %s size must be positive", name);
+    if (elem != 4 && elem != 2) return fail(VQM_ERR_VALUE, "element size must be 4 (fp32) or 2 (fp16)");
+    if (device_ptr == nullptr || (reinterpret_cast<uintptr_t>(device_ptr) & 15u) != 0)
+        return fail(VQM_ERR_VALUE, "%s: device pointer must be 16-byte aligned", name);
+    auto it = rt->buffers.find(name);
+    if (it != rt->buffers.end()) {
+        cudaStreamSynchronize(rt->stream);
+        release(it->second);
+        rt->buffers.erase(it);
+    }
+    Buffer b;
+    b.data = device_ptr;
+    b.n = n;
+    b.elem = elem;
+    b.owned = false;
+    rt->buffers[name] = b;
+    return VQM_OK;
+}
+
+int vqm_release(vqm_runtime *rt, const char *name) {
+    auto it = rt->buffers.find(name);
+    if (it == rt->buffers.end()) return fail(VQM_ERR_KEY, "device buffer %s is not allocated", name);
+    cudaStreamSynchronize(rt->stream);
+    release(it->second);
+    rt->buffers.erase(it);
+    return VQM_OK;
+}
+
+int vqm_write(vqm_runtime *rt, const char *name, const void *data, size_t nbytes, size_t offset) {
+    int rc = VQM_OK;
+    Buffer *b = find_any_buffer(rt, name, &rc);
+    if (b == nullptr) return rc;
+    if (nbytes % b->elem != 0 || offset > b->n || nbytes / b->elem > b->n - offset)
+        return fail(VQM_ERR_VALUE, "write to %s: bad offset/size for %d-byte elements", name, b->elem);
+    if ((rc = no_capture(rt, "write")) != VQM_OK) return rc;
+    cudaError_t err = cudaMemcpyAsync(static_cast<char *>(b->data) + offset * b->elem, data, nbytes, cudaMemcpyHostToDevice, rt->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+    if (err != cudaSuccess) return cuda_fail("buffer write", err);
+    return VQM_OK;
+}
+
+int vqm_read(vqm_runtime *rt, const char *name, void *out, size_t n, size_t offset) {
+    int rc = VQM_OK;
+    Buffer *b = find_any_buffer(rt, name, &rc);
+    if (b == nullptr) return rc;
+    if (offset > b->n) return fail(VQM_ERR_VALUE, "bad read offset");
+    if (n > b->n - offset) return fail(VQM_ERR_VALUE, "read of %zu elements exceeds buffer %s", n, name);
+    if ((rc = no_capture(rt, "read")) != VQM_OK) return rc;
+    cudaError_t err = cudaMemcpyAsync(out, static_cast<char *>(b->data) + offset * b->elem, n * b->elem, cudaMemcpyDeviceToHost, rt->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+    if (err != cudaSuccess) return cuda_fail("buffer read", err);
+    return VQM_OK;
+}
+
+int vqm_copy(vqm_runtime *rt, const char *dst, size_t dst_off, const char *src, size_t src_off, size_t n) {
+    int rc = VQM_OK;
+    Buffer *d = find_any_buffer(rt, dst, &rc);
+    if (d == nullptr) return rc;
+    Buffer *s = find_any_buffer(rt, src, &rc);
+    if (s == nullptr) return rc;
+    if (d->elem != s->elem) return fail(VQM_ERR_TYPE, "copy between buffers of different precision");
+    if (dst_off > d->n || n > d->n - dst_off || src_off > s->n || n > s->n - src_off)
+        return fail(VQM_ERR_VALUE, "copy out of bounds (%s <- %s)", dst, src);
+    const size_t e = static_cast<size_t>(d->elem);
+    const cudaError_t err = cudaMemcpyAsync(static_cast<char *>(d->data) + dst_off * e, static_cast<char *>(s->data) + src_off * e,
+                                            n * e, cudaMemcpyDeviceToDevice, rt->stream);
+    if (err != cudaSuccess) return cuda_fail("buffer copy", err);
+    return VQM_OK;
+}
+
+int vqm_zero_range(vqm_runtime *rt, const char *name, size_t offset, size_t n) {
+    int rc = VQM_OK;
+    Buffer *b = find_any_buffer(rt, name, &rc);
+    if (b == nullptr) return rc;
+    if (offset > b->n || n > b->n - offset) return fail(VQM_ERR_VALUE, "zero_range out of bounds");
+    const cudaError_t err = cudaMemsetAsync(static_cast<char *>(b->data) + offset * b->elem, 0, n * b->elem, rt->stream);
+    if (err != cudaSuccess) return cuda_fail("cudaMemset", err);
+    return VQM_OK;
+}
+
+int vqm_zero(vqm_runtime *rt, const char *name) {
+    int rc = VQM_OK;
+    Buffer *b = find_any_buffer(rt, name, &rc);
+    if (b == nullptr) return rc;
+    return vqm_zero_range(rt, name, 0, b->n);
+}
+
+int vqm_buffer_ptr(vqm_runtime *rt, const char *name, uint64_t *addr, size_t *n) {
+    int rc = VQM_OK;
+    float *p = find_f32(rt, name, 0, &rc);
+    if (p == nullptr) return rc;
+    *addr = reinterpret_cast<uintptr_t>(p);
+    *n = rt->buffers[name].n;
+    return VQM_OK;
+}
+
+int vqm_buffer_elem(vqm_runtime *rt, const char *name, int *elem) {
+    int rc = VQM_OK;
+    Buffer *b = find_any_buffer(rt, name, &rc);
+    if (b == nullptr) return rc;
+    *elem = b->elem;
+    return VQM_OK;
+}
+
+int vqm_buffer_len(vqm_runtime *rt, const char *name, size_t *n) {
+    int rc = VQM_OK;
+    Buffer *b = find_any_buffer(rt, name, &rc);
+    if (b == nullptr) return rc;
+    *n = b->n;
+    return VQM_OK;
+}
+
+int vqm_buffer_bytes(vqm_runtime *rt, size_t *out) {
+    size_t total = 0;
+    for (auto &kv : rt->buffers) total += kv.second.bytes();
+    *out = total;
+    return VQM_OK;
+}
+
+int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok) {
+    if (ntok < 1) return fail(VQM_ERR_VALUE, "ntok must be positive");
+    int rc = VQM_OK;
+    Tensor *t = find_tensor(rt, weight, &rc);
+    if (t == nullptr) return rc;
+    if (t->cols % 32 != 0) return fail(VQM_ERR_VALUE, "%s: matvec cols must be a multiple of 32", weight);
+    const float *xp = find_f32(rt, x, static_cast<size_t>(t->cols) * ntok, &rc);
+    if (xp == nullptr) return rc;
+    float *yp = find_f32(rt, y, static_cast<size_t>(t->rows) * ntok, &rc);
+    if (yp == nullptr) return rc;
+    // every group of 8 activation rows re-reads the weight (from L2 when it fits)
+    for (int c = 0; c < ntok; c += 8) {
+        const int m = ntok - c < 8 ? ntok - c : 8;
+        rc = launch_group(rt, *t, xp + static_cast<size_t>(c) * t->cols, yp + static_cast<size_t>(c) * t->rows, m, false);
+        if (rc != VQM_OK) return rc;
+    }
+    return VQM_OK;
+}
+
+int vqm_qmv_argmax(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int *out_ids) {
+    if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8] for the fused argmax");
+    int rc = VQM_OK;
+    Tensor *t = find_tensor(rt, weight, &rc);
+    if (t == nullptr) return rc;
+    if (t->cols % 32 != 0) return fail(VQM_ERR_VALUE, "%s: matvec cols must be a multiple of 32", weight);
+    const float *xp = find_f32(rt, x, static_cast<size_t>(t->cols) * ntok, &rc);
+    if (xp == nullptr) return rc;
+    float *yp = nullptr;
+    if (y != nullptr) {
+        yp = find_f32(rt, y, static_cast<size_t>(t->rows) * ntok, &rc);
+        if (yp == nullptr) return rc;
+    }
+    if (out_ids != nullptr && (rc = no_capture(rt, "a blocking qmv_argmax")) != VQM_OK) return rc;
+    if ((rc = launch_group(rt, *t, xp, yp, ntok, true)) != VQM_OK) return rc;
+    if (out_ids != nullptr) {
+        cudaError_t err = cudaMemcpyAsync(out_ids, rt->argmax_ids, sizeof(int) * ntok, cudaMemcpyDeviceToHost, rt->stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+        if (err != cudaSuccess) return cuda_fail("qmv_argmax", err);
+    }
+    return VQM_OK;
+}
+
+int vqm_argmax_result(vqm_runtime *rt, uint64_t *ids_addr, uint64_t *values_addr) {
+    if (ids_addr != nullptr) *ids_addr = reinterpret_cast<uintptr_t>(rt->argmax_ids);
+    if (values_addr != nullptr) *values_addr = reinterpret_cast<uintptr_t>(rt->argmax_vals);
+    return VQM_OK;
+}
+
+int vqm_set_argmax_row_base(vqm_runtime *rt, const char *weight, int row_base) {
+    int rc = VQM_OK;
+    Tensor *t = find_tensor(rt, weight, &rc);
+    if (t == nullptr) return rc;
+    if (row_base < 0) return fail(VQM_ERR_VALUE, "row_base must be >= 0");
+    t->argmax_row_base = row_base;
+    return VQM_OK;
+}
+
+int vqm_matvec(vqm_runtime *rt, const char *weight, const float *x_host, size_t x_bytes, float *y_host, size_t y_bytes) {
+    auto it = rt->tensors.find(weight);
+    if (it == rt->tensors.end()) return fail(VQM_ERR_KEY, "%s is not resident on the GPU", weight);
+    const Tensor &t = it->second;
+    if (x_bytes != static_cast<size_t>(t.cols) * sizeof(float))
+        return fail(VQM_ERR_VALUE, "%s: x has %zu bytes, expected %d float32", weight, x_bytes, t.cols);
+    if (y_bytes < static_cast<size_t>(t.rows) * sizeof(float))
+        return fail(VQM_ERR_VALUE, "%s: y has room for %zu bytes, need %zu", weight, y_bytes, static_cast<size_t>(t.rows) * sizeof(float));
+    if (t.cols % 32 != 0) return fail(VQM_ERR_VALUE, "%s: matvec cols must be a multiple of 32", weight);
+    int rc = no_capture(rt, "matvec");
+    if (rc != VQM_OK) return rc;
+    cudaError_t err = cudaSuccess;
+    if (rt->scratch_x_n < static_cast<size_t>(t.cols)) {
+        cudaFree(rt->scratch_x);
+        rt->scratch_x = nullptr;
+        rt->scratch_x_n = 0;
+        err = cudaMalloc(&rt->scratch_x, sizeof(float) * t.cols);
+        if (err == cudaSuccess) rt->scratch_x_n = t.cols;
+    }
+    if (err == cudaSuccess && rt->scratch_y_n < static_cast<size_t>(t.rows)) {
+        cudaFree(rt->scratch_y);
+        rt->scratch_y = nullptr;
+        rt->scratch_y_n = 0;
+        err = cudaMalloc(&rt->scratch_y, sizeof(float) * t.rows);
+        if (err == cudaSuccess) rt->scratch_y_n = t.rows;
+    }
+    if (err != cudaSuccess) return cuda_fail("scratch allocation", err);
+    err = cudaMemcpyAsync(rt->scratch_x, x_host, x_bytes, cudaMemcpyHostToDevice, rt->stream);
+    if (err != cudaSuccess) return cuda_fail("qmatvec H2D", err);
+    if ((rc = launch_group(rt, t, rt->scratch_x, rt->scratch_y, 1, false)) != VQM_OK) return rc;
+    err = cudaMemcpyAsync(y_host, rt->scratch_y, sizeof(float) * t.rows, cudaMemcpyDeviceToHost, rt->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+    if (err != cudaSuccess) return cuda_fail("qmatvec", err);
+    return check_status_word(rt, "qmatvec");
+}
+
+int vqm_argmax_rows(vqm_runtime *rt, const char *x, int n, int ntok, int *out) {
+    if (ntok < 1 || ntok > 256) return fail(VQM_ERR_VALUE, "ntok must be in [1, %d]", 256);
+    if (n < 1) return fail(VQM_ERR_VALUE, "n must be positive");
+    int rc = VQM_OK;
+    const float *xp = find_f32(rt, x, static_cast<size_t>(n) * ntok, &rc);
+    if (xp == nullptr) return rc;
+    if ((rc = no_capture(rt, "argmax")) != VQM_OK) return rc;
+    cudaError_t err = vqm::launch_argmax_rows(xp, n, ntok, rt->argmax_ids, rt->stream);
+    if (err == cudaSuccess) {
+        count_launch(rt);
+        err = cudaMemcpyAsync(out, rt->argmax_ids, sizeof(int) * ntok, cudaMemcpyDeviceToHost, rt->stream);
+    }
+    if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+    if (err != cudaSuccess) return cuda_fail("argmax_rows", err);
+    return VQM_OK;
+}
+
+int vqm_argmax(vqm_runtime *rt, const char *x, int n, int *out) { return vqm_argmax_rows(rt, x, n, 1, out); }
+
+int vqm_dequantize(vqm_runtime *rt, const char *weight, const char *out) {
+    int rc = VQM_OK;
+    Tensor *t = find_tensor(rt, weight, &rc);
+    if (t == nullptr) return rc;
+    const size_t numel = static_cast<size_t>(t->rows) * t->cols;
+    if (numel % 8 != 0) return fail(VQM_ERR_VALUE, "%s: element count must be a multiple of 8", weight);
+    float *op = find_f32(rt, out, numel, &rc);
+    if (op == nullptr) return rc;
+    const uint8_t *cb = codebook_for(rt, t->type);
+    if (vqm::grid_is_codebook(t->type) && cb == nullptr)
+        return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t->type);
+    const cudaError_t err = vqm::launch_dequant(t->type, t->data, op, static_cast<long long>(numel), cb, rt->stream);
+    if (err != cudaSuccess) return cuda_fail("dequantize launch", err);
+    count_launch(rt);
+    return VQM_OK;
+}
+
+int vqm_set_gemm_min_rows(vqm_runtime *rt, int n) {
+    if (n < 0) return fail(VQM_ERR_VALUE, "gemm_min_rows must be >= 0");
+    rt->gemm_min_rows = n;
+    return VQM_OK;
+}
+
+int vqm_synchronize(vqm_runtime *rt) {
+    const int rc = no_capture(rt, "synchronize");
+    if (rc != VQM_OK) return rc;
+    const cudaError_t err = cudaDeviceSynchronize();
+    if (err != cudaSuccess) return cuda_fail("synchronize", err);
+    return check_status_word(rt, "synchronize");
+}
+
+int vqm_mem_info(size_t *free_bytes, size_t *total_bytes) {
+    const cudaError_t err = cudaMemGetInfo(free_bytes, total_bytes);
+    if (err != cudaSuccess) return cuda_fail("cudaMemGetInfo", err);
+    return VQM_OK;
+}
+
+void *vqm_stream(vqm_runtime *rt) { return rt->stream; }
+
+int vqm_capture_begin(vqm_runtime *rt) {
+    if (rt->capturing) return fail(VQM_ERR_VALUE, "a capture is already open");
+    const cudaError_t err = cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeThreadLocal);
+    if (err != cudaSuccess) return cuda_fail("cudaStreamBeginCapture", err);
+    rt->capturing = true;
+    rt->capture_launches = 0;
+    return VQM_OK;
+}
+
+int vqm_capture_end(vqm_runtime *rt, int *graph_id) {
+    if (!rt->capturing) return fail(VQM_ERR_VALUE, "no capture is open");
+    rt->capturing = false;
+    cudaGraph_t graph = nullptr;
+    cudaError_t err = cudaStreamEndCapture(rt->stream, &graph);
+    if (err != cudaSuccess) return cuda_fail("cudaStreamEndCapture", err);
+    Graph g;
+    err = cudaGraphInstantiate(&g.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (err != cudaSuccess) return cuda_fail("cudaGraphInstantiate", err);
+    g.kernels = rt->capture_launches;
+    rt->graphs.push_back(g);
+    *graph_id = static_cast<int>(rt->graphs.size()) - 1;
+    return VQM_OK;
+}
+
+int vqm_graph_launch(vqm_runtime *rt, int graph_id) {
+    if (graph_id < 0 || graph_id >= static_cast<int>(rt->graphs.size()) || rt->graphs[graph_id].exec == nullptr)
+        return fail(VQM_ERR_KEY, "unknown graph %d", graph_id);
+    const cudaError_t err = cudaGraphLaunch(rt->graphs[graph_id].exec, rt->stream);
+    if (err != cudaSuccess) return cuda_fail("cudaGraphLaunch", err);
+    count_launch(rt, rt->graphs[graph_id].kernels);
+    return VQM_OK;
+}
+
+int vqm_graph_destroy(vqm_runtime *rt, int graph_id) {
+    if (graph_id < 0 || graph_id >= static_cast<int>(rt->graphs.size()) || rt->graphs[graph_id].exec == nullptr)
+        return fail(VQM_ERR_KEY, "unknown graph %d", graph_id);
+    cudaStreamSynchronize(rt->stream);
+    cudaGraphExecDestroy(rt->graphs[graph_id].exec);
+    rt->graphs[graph_id].exec = nullptr;
+    return VQM_OK;
+}
+
+int vqm_launch_count(vqm_runtime *rt, uint64_t *out) {
+    *out = rt->launches;
+    return VQM_OK;
+}
+
+int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
+                unsigned *status, void *stream) {
+    size_t row_bytes = 0;
+    const int rc = check_shape("w", type, cols, rows, &row_bytes);
+    if (rc != VQM_OK) return rc;
+    if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8]");
+    if (cols % 32 != 0) return fail(VQM_ERR_VALUE, "matvec cols must be a multiple of 32");
+    if (w == nullptr || x == nullptr || y == nullptr || status == nullptr) return fail(VQM_ERR_VALUE, "null pointer");
+    if (((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) != 0)
+        return fail(VQM_ERR_VALUE, "w, x and y must be 16-byte aligned");
+    if (vqm::grid_is_codebook(type) && codebook == nullptr) return fail(VQM_ERR_VALUE, "GGUF type %d needs its codebook", type);
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaError_t err = cudaGetDevice(&dev);
+        if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return cuda_fail("device query", err);
+    }
+    vqm::MatvecArgs a{};
+    a.w = static_cast<const uint8_t *>(w);
+    a.x = x;
+    a.y = y;
+    a.codebook = static_cast<const uint8_t *>(codebook);
+    a.status = status;
+    a.rows = rows;
+    a.cols = cols;
+    a.row_bytes = static_cast<long long>(row_bytes);
+    const cudaError_t err = dispatch_qmv(type, a, ntok, pick_rw(rows, sm_count), sm_count, static_cast<cudaStream_t>(stream), nullptr);
+    if (err != cudaSuccess) return cuda_fail("qmv launch", err);
+    return VQM_OK;
+}
+
+}  // extern "C"
