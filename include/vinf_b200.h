@@ -114,6 +114,8 @@ int vqm_argmax_rows(vqm_runtime *rt, const char *x, int n, int ntok, int *out);
 int vqm_qmv_argmax(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int *out_ids);
 /* Device arrays holding the last fused argmax: ids[8] (int32) and values[8] (fp32). */
 int vqm_argmax_result(vqm_runtime *rt, uint64_t *ids_addr, uint64_t *values_addr);
+/* Blocking copy of the first ntok ids (and, if values is not NULL, values) of the last fused argmax to the host. */
+int vqm_argmax_fetch(vqm_runtime *rt, int ntok, int *ids, float *values);
 /* Row offset added to the ids of the fused argmax (for a runtime that holds rows [base, base + rows) of a
  * row-sharded LM head). */
 int vqm_set_argmax_row_base(vqm_runtime *rt, const char *weight, int row_base);
@@ -132,6 +134,9 @@ int vqm_mem_info(size_t *free_bytes, size_t *total_bytes);
 
 /* The runtime's stream (a cudaStream_t), so that a caller can record events on it or order other work. */
 void *vqm_stream(vqm_runtime *rt);
+/* Makes the runtime launch on a stream the caller owns (for instance the stream another library is
+ * capturing into a graph, or one that also carries NCCL collectives); NULL restores the runtime's own. */
+int vqm_set_stream(vqm_runtime *rt, void *stream);
 /* Records the launches made between begin and end into a CUDA graph instead of running them (a whole
  * decoder pass of qmv calls becomes one launch).  Blocking entry points are not allowed in between. */
 int vqm_capture_begin(vqm_runtime *rt);

@@ -6,10 +6,12 @@ CPU or PyTorch fallback.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_char_p, c_int, c_size_t, c_uint64, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libvinf_b200.so"
+# VINF_B200_LIB points at another build of the same library (a debug or experimental build)
+LIB_PATH = Path(os.environ.get("VINF_B200_LIB") or Path(__file__).resolve().parent / "libvinf_b200.so")
 
 OK, ERR_KEY, ERR_VALUE, ERR_TYPE, ERR_MEMORY, ERR_CUDA = range(6)
 
@@ -53,12 +55,14 @@ SIGNATURES: dict[str, list] = {
     "vqm_argmax_rows": [c_void_p, c_char_p, c_int, c_int, POINTER(c_int)],
     "vqm_qmv_argmax": [c_void_p, c_char_p, c_char_p, c_char_p, c_int, POINTER(c_int)],
     "vqm_argmax_result": [c_void_p, POINTER(c_uint64), POINTER(c_uint64)],
+    "vqm_argmax_fetch": [c_void_p, c_int, POINTER(c_int), POINTER(ctypes.c_float)],
     "vqm_set_argmax_row_base": [c_void_p, c_char_p, c_int],
     "vqm_dequantize": [c_void_p, c_char_p, c_char_p],
     "vqm_set_gemm_min_rows": [c_void_p, c_int],
     "vqm_synchronize": [c_void_p],
     "vqm_mem_info": [POINTER(c_size_t), POINTER(c_size_t)],
     "vqm_stream": [c_void_p],
+    "vqm_set_stream": [c_void_p, c_void_p],
     "vqm_capture_begin": [c_void_p],
     "vqm_capture_end": [c_void_p, POINTER(c_int)],
     "vqm_graph_launch": [c_void_p, c_int],

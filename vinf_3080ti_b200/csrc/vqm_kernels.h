@@ -26,13 +26,13 @@ struct MatvecArgs {
 
 enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1 };
 
-// One launcher per GGUF type (vqm_matvec_type.cu).  m: activation rows (1..8); rw: preferred rows per warp
-// row group; sm_count: SMs of the device; grid_out (optional) receives the grid size used.
+// One launcher per GGUF type (vqm_matvec_type.cu).  m: activation rows (1..8); sm_count: SMs of the device;
+// grid_out (optional) receives the grid size used.
 #define VQM_FOR_EACH_TYPE(X) \
     X(0, F32) X(1, F16) X(8, Q8_0) X(10, Q2_K) X(11, Q3_K) X(12, Q4_K) X(13, Q5_K) X(14, Q6_K) X(16, IQ2_XXS) \
     X(17, IQ2_XS) X(18, IQ3_XXS) X(20, IQ4_NL) X(21, IQ3_S) X(22, IQ2_S) X(23, IQ4_XS)
 #define VQM_DECLARE_LAUNCHER(id, name) \
-    cudaError_t launch_qmv_##name(const MatvecArgs &a, int m, int rw, int sm_count, cudaStream_t stream, int *grid_out);
+    cudaError_t launch_qmv_##name(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out);
 VQM_FOR_EACH_TYPE(VQM_DECLARE_LAUNCHER)
 #undef VQM_DECLARE_LAUNCHER
 

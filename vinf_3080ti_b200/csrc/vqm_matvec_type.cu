@@ -10,9 +10,19 @@
 namespace vqm {
 namespace {
 
-template <int M, int RW>
+// Rows a warp takes per chunk: 8 for one or two activation rows (more independent work per staged
+// activation load), 4 beyond that (registers), 2 where eight-row stages of a wide type do not fit.
+template <int M>
+constexpr int rows_per_chunk() {
+    constexpr int want = M <= 2 ? 8 : 4;
+    return matvec_smem_bytes_for<VQM_TYPE, want, M>() <= 100 * 1024 ? want
+         : matvec_smem_bytes_for<VQM_TYPE, want / 2, M>() <= 200 * 1024 ? want / 2 : want / 4;
+}
+
+template <int M>
 cudaError_t launch_one(const MatvecArgs &a, int sm_count, cudaStream_t stream, int *grid_out) {
-    constexpr size_t smem = matvec_smem_bytes(VQM_TYPE, RW);
+    constexpr int RW = rows_per_chunk<M>();
+    constexpr size_t smem = matvec_smem_bytes_for<VQM_TYPE, RW, M>();
     static int blocks_per_sm = 0;  // one device per process
     if (blocks_per_sm == 0) {
         cudaError_t err = cudaFuncSetAttribute(qmv_kernel<VQM_TYPE, M, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -23,27 +33,13 @@ cudaError_t launch_one(const MatvecArgs &a, int sm_count, cudaStream_t stream, i
         if (err != cudaSuccess) return err;
         blocks_per_sm = n > 0 ? n : 1;
     }
-    const int n_rg = (a.rows + RW - 1) / RW;
+    // one wave; a short tensor gets fewer blocks so that every warp still has a row
     int grid = sm_count * blocks_per_sm;
-    if (grid > n_rg) grid = n_rg;
+    const int want = (a.rows + kWarps - 1) / kWarps;
+    if (grid > want) grid = want;
     if (grid_out != nullptr) *grid_out = grid;
     qmv_kernel<VQM_TYPE, M, RW><<<grid, kWarps * 32, smem, stream>>>(a);
     return cudaGetLastError();
-}
-
-template <int RW>
-cudaError_t launch_m(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out) {
-    switch (m) {
-        case 1: return launch_one<1, RW>(a, sm_count, stream, grid_out);
-        case 2: return launch_one<2, RW>(a, sm_count, stream, grid_out);
-        case 3: return launch_one<3, RW>(a, sm_count, stream, grid_out);
-        case 4: return launch_one<4, RW>(a, sm_count, stream, grid_out);
-        case 5: return launch_one<5, RW>(a, sm_count, stream, grid_out);
-        case 6: return launch_one<6, RW>(a, sm_count, stream, grid_out);
-        case 7: return launch_one<7, RW>(a, sm_count, stream, grid_out);
-        case 8: return launch_one<8, RW>(a, sm_count, stream, grid_out);
-        default: return cudaErrorInvalidValue;
-    }
 }
 
 }  // namespace
@@ -51,11 +47,18 @@ cudaError_t launch_m(const MatvecArgs &a, int m, int sm_count, cudaStream_t stre
 #define VQM_CAT2(a, b) a##b
 #define VQM_CAT(a, b) VQM_CAT2(a, b)
 
-// rw: rows per warp row group (2 or 4; wide unquantised rows only fit 2).
-cudaError_t VQM_CAT(launch_qmv_, VQM_TYPE_NAME)(const MatvecArgs &a, int m, int rw, int sm_count, cudaStream_t stream,
-                                                int *grid_out) {
-    if (rw >= 4 && matvec_smem_bytes(VQM_TYPE, 4) <= 200 * 1024) return launch_m<4>(a, m, sm_count, stream, grid_out);
-    return launch_m<2>(a, m, sm_count, stream, grid_out);
+cudaError_t VQM_CAT(launch_qmv_, VQM_TYPE_NAME)(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out) {
+    switch (m) {
+        case 1: return launch_one<1>(a, sm_count, stream, grid_out);
+        case 2: return launch_one<2>(a, sm_count, stream, grid_out);
+        case 3: return launch_one<3>(a, sm_count, stream, grid_out);
+        case 4: return launch_one<4>(a, sm_count, stream, grid_out);
+        case 5: return launch_one<5>(a, sm_count, stream, grid_out);
+        case 6: return launch_one<6>(a, sm_count, stream, grid_out);
+        case 7: return launch_one<7>(a, sm_count, stream, grid_out);
+        case 8: return launch_one<8>(a, sm_count, stream, grid_out);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace vqm

@@ -64,7 +64,8 @@ const int kCodebookTypes[5] = {vqm::kIQ2_XXS, vqm::kIQ2_XS, vqm::kIQ2_S, vqm::kI
 struct vqm_runtime {
     int device = 0;
     int sm_count = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;      // the stream in use
+    cudaStream_t own_stream = nullptr;  // the one the runtime created
     std::unordered_map<std::string, Tensor> tensors;
     std::unordered_map<std::string, Buffer> buffers;
     uint8_t *codebooks[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -144,18 +145,15 @@ void count_launch(vqm_runtime *rt, uint64_t n = 1) {
     else rt->launches += n;
 }
 
-cudaError_t dispatch_qmv(int type, const vqm::MatvecArgs &a, int m, int rw, int sm_count, cudaStream_t stream, int *grid) {
+cudaError_t dispatch_qmv(int type, const vqm::MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid) {
     switch (type) {
 #define VQM_CASE(id, name) \
-    case id: return vqm::launch_qmv_##name(a, m, rw, sm_count, stream, grid);
+    case id: return vqm::launch_qmv_##name(a, m, sm_count, stream, grid);
         VQM_FOR_EACH_TYPE(VQM_CASE)
 #undef VQM_CASE
         default: return cudaErrorInvalidValue;
     }
 }
-
-// Rows per warp row group: 4 when that still gives every warp of a full grid some work, else 2.
-int pick_rw(int rows, int sm_count) { return rows / 4 >= sm_count * 8 ? 4 : 2; }
 
 int check_shape(const char *name, int type, int cols, int rows, size_t *row_bytes) {
     const vqm::Traits t = vqm::traits_of(type);
@@ -188,7 +186,7 @@ int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int
         a.out_val = rt->argmax_vals;
         a.row_base = t.argmax_row_base;
     }
-    const cudaError_t err = dispatch_qmv(t.type, a, m, pick_rw(t.rows, rt->sm_count), rt->sm_count, rt->stream, nullptr);
+    const cudaError_t err = dispatch_qmv(t.type, a, m, rt->sm_count, rt->stream, nullptr);
     if (err != cudaSuccess) return cuda_fail("qmv launch", err);
     count_launch(rt);
     return VQM_OK;
@@ -220,7 +218,8 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
     vqm_runtime *rt = new vqm_runtime();
     cudaError_t err = cudaGetDevice(&rt->device);
     if (err == cudaSuccess) err = cudaDeviceGetAttribute(&rt->sm_count, cudaDevAttrMultiProcessorCount, rt->device);
-    if (err == cudaSuccess) err = cudaStreamCreate(&rt->stream);
+    if (err == cudaSuccess) err = cudaStreamCreate(&rt->own_stream);
+    rt->stream = rt->own_stream;
     if (err == cudaSuccess) err = cudaMalloc(&rt->status, 256);
     if (err == cudaSuccess) err = cudaMemset(rt->status, 0, 256);
     if (err == cudaSuccess) err = cudaMalloc(&rt->part_val, sizeof(float) * 8 * vqm::kMaxGrid);
@@ -247,6 +246,7 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
 void vqm_runtime_destroy(vqm_runtime *rt) {
     if (rt == nullptr) return;
     if (rt->stream != nullptr) cudaStreamSynchronize(rt->stream);
+    rt->stream = rt->own_stream;
     for (auto &g : rt->graphs)
         if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
     for (auto &kv : rt->tensors) release(kv.second);
@@ -560,6 +560,18 @@ int vqm_argmax_result(vqm_runtime *rt, uint64_t *ids_addr, uint64_t *values_addr
     return VQM_OK;
 }
 
+int vqm_argmax_fetch(vqm_runtime *rt, int ntok, int *ids, float *values) {
+    if (ntok < 1 || ntok > 8 || ids == nullptr) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8] and ids not NULL");
+    const int rc = no_capture(rt, "argmax_fetch");
+    if (rc != VQM_OK) return rc;
+    cudaError_t err = cudaMemcpyAsync(ids, rt->argmax_ids, sizeof(int) * ntok, cudaMemcpyDeviceToHost, rt->stream);
+    if (err == cudaSuccess && values != nullptr)
+        err = cudaMemcpyAsync(values, rt->argmax_vals, sizeof(float) * ntok, cudaMemcpyDeviceToHost, rt->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+    if (err != cudaSuccess) return cuda_fail("argmax_fetch", err);
+    return VQM_OK;
+}
+
 int vqm_set_argmax_row_base(vqm_runtime *rt, const char *weight, int row_base) {
     int rc = VQM_OK;
     Tensor *t = find_tensor(rt, weight, &rc);
@@ -663,6 +675,13 @@ int vqm_mem_info(size_t *free_bytes, size_t *total_bytes) {
 
 void *vqm_stream(vqm_runtime *rt) { return rt->stream; }
 
+int vqm_set_stream(vqm_runtime *rt, void *stream) {
+    const int rc = no_capture(rt, "set_stream");
+    if (rc != VQM_OK) return rc;
+    rt->stream = stream != nullptr ? static_cast<cudaStream_t>(stream) : rt->own_stream;
+    return VQM_OK;
+}
+
 int vqm_capture_begin(vqm_runtime *rt) {
     if (rt->capturing) return fail(VQM_ERR_VALUE, "a capture is already open");
     const cudaError_t err = cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeThreadLocal);
@@ -738,7 +757,7 @@ int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, flo
     a.rows = rows;
     a.cols = cols;
     a.row_bytes = static_cast<long long>(row_bytes);
-    const cudaError_t err = dispatch_qmv(type, a, ntok, pick_rw(rows, sm_count), sm_count, static_cast<cudaStream_t>(stream), nullptr);
+    const cudaError_t err = dispatch_qmv(type, a, ntok, sm_count, static_cast<cudaStream_t>(stream), nullptr);
     if (err != cudaSuccess) return cuda_fail("qmv launch", err);
     return VQM_OK;
 }

@@ -221,6 +221,13 @@ class Runtime:
         _capi.check(self._lib.vqm_argmax_result(self._h, ctypes.byref(ids), ctypes.byref(vals)))
         return ids.value, vals.value
 
+    def argmax_fetch(self, ntok: int, with_values: bool = False):
+        """Blocking read of the last fused argmax: ids, or (ids, values)."""
+        ids = (ctypes.c_int * ntok)()
+        vals = (ctypes.c_float * ntok)() if with_values else None
+        _capi.check(self._lib.vqm_argmax_fetch(self._h, int(ntok), ids, vals))
+        return (list(ids), list(vals)) if with_values else list(ids)
+
     def set_argmax_row_base(self, weight: str, row_base: int) -> None:
         _capi.check(self._lib.vqm_set_argmax_row_base(self._h, _name(weight), int(row_base)))
 
@@ -243,6 +250,10 @@ class Runtime:
     def stream(self) -> int:
         """The runtime's cudaStream_t as an integer (wrap with torch.cuda.ExternalStream to time on it)."""
         return int(self._lib.vqm_stream(self._h) or 0)
+
+    def set_stream(self, stream: int | None) -> None:
+        """Launch on a caller-owned cudaStream_t (None: back to the runtime's own stream)."""
+        _capi.check(self._lib.vqm_set_stream(self._h, ctypes.c_void_p(stream) if stream else None))
 
     def capture_begin(self) -> None:
         _capi.check(self._lib.vqm_capture_begin(self._h))
