@@ -1,0 +1,402 @@
+"""Benchmark of the GGUF quantized-matvec path:  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): one decode pass over the synthetic 27B matvec set at M activation rows (default 4, the
+MTP k=3 verify pass): 64 layers x {Q6_K q/k/v/o, Q3_K gate/up, Q4_K down} with hidden 5120 / FFN 17408,
+then the Q6_K LM head 151936 x 5120 with the fused on-device argmax - 449 matvec launches over
+12.6 GB of raw GGUF blocks, all resident in HBM.  Weights are seeded synthetic blocks (uniform-random
+bytes, fp16 super-scales uniform in [1e-3, 1e-2)), activations fp32 N(0,1).  The pass is 100x larger than L2,
+so no flush is needed between steps.
+
+metric / value   weight GB/s of the pass (weight bytes / device time), kernel-side, inputs resident in HBM
+e2e              the same through the public Runtime API with host buffers: per step the activations are
+                 copied from pinned host memory, the pass runs, the argmax ids are read back
+roofline         the dominant kernel (Q3_K gate/up matvec) timed alone over the model's 128 distinct tensors
+cpu_baseline     the reference's own CPU matvec (oracle/_ref, built from the reference's qwen_cpu.c) on a
+                 bounded sample of the same pass, on this host's cores
+N > 1 (torchrun) every rank owns a contiguous slice of the output rows of every tensor (strong scaling); outputs
+                 are combined with NCCL all-gathers, the argmax with an all-gather of (value, index) pairs.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+from vinf_3080ti_b200.gguf_types import F16_FIELDS, TRAITS, GGUFTensorType as T  # noqa: E402
+from vinf_3080ti_b200.synth import LAYER_SET, LM_HEAD, N_LAYERS, synthetic_activations, synthetic_blocks, tensor_bytes  # noqa: E402
+
+METRIC = "quant-matvec weight GB/s, synthetic-27B decode pass"
+# DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/qmv_Q3_K_17408x5120_M4.md); None until measured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+# ---- helpers ---------------------------------------------------------------------------------------------
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for line in self.lines:
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [v for v in sm if v > 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous slice [begin, end) of the output rows owned by `rank`; the start stays even so that the
+    slice of a 2-byte-aligned block format begins on a 4-byte boundary like the full tensor's rows."""
+    per = (rows // world) & ~1
+    begin = rank * per
+    end = rows if rank == world - 1 else begin + per
+    return begin, end
+
+
+def pass_tensors() -> list[tuple[str, T, int, int]]:
+    out = []
+    for layer in range(N_LAYERS):
+        for name, t, rows, cols in LAYER_SET:
+            out.append((f"blk.{layer}.{name}", t, rows, cols))
+    out.append((LM_HEAD[0],) + LM_HEAD[1:])
+    return out
+
+
+# ---- the CPU arm -----------------------------------------------------------------------------------------
+
+class CpuArm:
+    """The reference's own CPU matvec (oracle/_ref, compiled from the reference's qwen_cpu.c) on a bounded sample
+    of the pass: one layer set (7 tensors) + the Q6_K LM head.  Falls back to the plain-C oracle port only if
+    the reference build is missing."""
+
+    def __init__(self, m: int, threads: int) -> None:
+        from tests import oracle_libs
+
+        self.m, self.threads = m, threads
+        mod = oracle_libs.load_reference_cpu_module()
+        self.kind = "reference" if mod is not None else "port"
+        with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
+            grid = z["iq3s_grid"].tobytes()
+        rng = np.random.default_rng(0)
+        sample = list(LAYER_SET) + [LM_HEAD]
+        self.nbytes = 0
+        self.keep = []
+        if mod is not None:
+            rt = mod.CpuRuntime(grid, threads)
+            for name, t, rows, cols in sample:
+                raw = synthetic_blocks(t, rows, cols, rng).tobytes()
+                self.keep.append(raw)
+                rt.add_tensor(name, raw, int(t), cols, rows)
+                rt.alloc(name + ".x", m * cols)
+                rt.alloc(name + ".y", m * rows)
+                rt.write(name + ".x", synthetic_activations(m, cols, rng).tobytes())
+                self.nbytes += len(raw)
+            self._pass = lambda: [rt.qmv(name, name + ".x", name + ".y", m) for name, *_ in sample]
+        else:
+            clib = oracle_libs.load_c_oracle()
+            mats = []
+            for name, t, rows, cols in sample:
+                raw = synthetic_blocks(t, rows, cols, rng)
+                mats.append((raw, t, rows, cols, synthetic_activations(m, cols, rng)))
+                self.nbytes += raw.size
+            self._pass = lambda: [oracle_libs.c_qmv(clib, raw, int(t), rows, cols, x) for raw, t, rows, cols, x in mats]
+        self.sample = (f"one layer set (Q6_K q/k/v/o, Q3_K gate/up, Q4_K down) + the Q6_K LM head at M={m}, "
+                       f"{self.nbytes} weight bytes per pass")
+
+    def one_pass(self) -> float:
+        t0 = time.perf_counter()
+        self._pass()
+        return time.perf_counter() - t0
+
+
+def cpu_baseline(m: int, seconds: float) -> dict:
+    threads = os.cpu_count() or 1
+    arm = CpuArm(m, threads)
+    arm.one_pass()
+    times = []
+    t_end = time.perf_counter() + seconds
+    while time.perf_counter() < t_end or len(times) < 2:
+        times.append(arm.one_pass())
+    return {"value": arm.nbytes / min(times) / 1e9, "unit": "GB/s", "cores": threads, "kind": arm.kind,
+            "sample": f"{arm.sample}; best of {len(times)} passes in ~{seconds:.0f} s"}
+
+
+def run_reference(args) -> None:
+    """--impl reference: the reference's CPU implementation of the path on this host's cores.  Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    threads = os.cpu_count() or 1
+    arm = CpuArm(args.m, threads)
+    for _ in range(max(1, args.warmup)):
+        arm.one_pass()
+    times = [arm.one_pass() for _ in range(args.steps)]
+    ms = 1e3 * sum(times) / len(times)
+    value = arm.nbytes / (ms * 1e-3) / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": max(1, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32 outputs; the reference CPU kernel rounds activations to int8 per 32 elements", "data": "synthetic",
+        "config": {"workload": f"synthetic-27B decode pass at M={args.m}; each step is a bounded sample of it: {arm.sample}",
+                   "activation_rows": args.m},
+        "tokens_per_s": None,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": arm.kind, "sample": arm.sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---- the GPU arm -----------------------------------------------------------------------------------------
+
+def run_gpu(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from vinf_3080ti_b200.runtime import Runtime
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    m = args.m
+    with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
+        books = {k: z[k].tobytes() for k in z.files}
+    rt = Runtime(books["iq3s_grid"], books)
+    stream = torch.cuda.ExternalStream(rt.stream(), device=dev)
+
+    # -- weights: seeded synthetic blocks generated on the device, this rank's row slice of every tensor
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    keep = []
+    weight_bytes_local = 0
+    weight_bytes_total = 0
+    tensors = pass_tensors()
+    local_rows: dict[str, tuple[int, int]] = {}
+    for name, t, rows, cols in tensors:
+        begin, end = shard_rows(rows, rank, world)
+        n = end - begin
+        block, size = TRAITS[t]
+        nblk = n * (cols // block)
+        raw = torch.randint(0, 256, (nblk * size + 256,), dtype=torch.uint8, device=dev, generator=gen)
+        blocks = raw[: nblk * size].view(nblk, size)
+        for off in F16_FIELDS[t]:
+            scale = torch.empty(nblk, dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=gen).to(torch.float16)
+            blocks[:, off : off + 2] = scale.view(torch.uint8).view(nblk, 2)
+        keep.append(raw)
+        rt.bind_tensor(name, raw.data_ptr(), int(t), cols, n)
+        local_rows[name] = (begin, end)
+        weight_bytes_local += nblk * size
+        weight_bytes_total += tensor_bytes(t, rows, cols)
+    rt.set_argmax_row_base(LM_HEAD[0], local_rows[LM_HEAD[0]][0])
+
+    # -- activations and outputs.  The synthetic pass has no ops between the matvecs, so every matvec of a given
+    #    input width reads the same activation buffer; outputs of all ranks are gathered into full-width buffers.
+    widths = sorted({cols for _, _, _, cols in tensors})
+    host_x = {w: torch.from_numpy(synthetic_activations(m, w, np.random.default_rng(w))).pin_memory() for w in widths}
+    dev_x = {w: torch.empty(m * w, dtype=torch.float32, device=dev) for w in widths}
+    for w in widths:
+        rt.bind(f"x{w}", dev_x[w].data_ptr(), m * w)
+        dev_x[w].copy_(host_x[w].view(-1))
+    out_rows = sorted({rows for _, _, rows, _ in tensors})
+    y_local = {r: torch.zeros(m * (shard_rows(r, rank, world)[1] - shard_rows(r, rank, world)[0]), dtype=torch.float32, device=dev)
+               for r in out_rows}
+    for r in out_rows:
+        rt.bind(f"y{r}", y_local[r].data_ptr(), y_local[r].numel())
+    gathered = {}
+    if world > 1:
+        for r in out_rows:
+            gathered[r] = [torch.empty_like(y_local[r]) if shard_rows(r, k, world)[1] - shard_rows(r, k, world)[0] ==
+                           shard_rows(r, rank, world)[1] - shard_rows(r, rank, world)[0] else
+                           torch.empty(m * (shard_rows(r, k, world)[1] - shard_rows(r, k, world)[0]), dtype=torch.float32, device=dev)
+                           for k in range(world)]
+        pair_local = torch.zeros(2 * 8, dtype=torch.float32, device=dev)
+        pair_all = [torch.empty_like(pair_local) for _ in range(world)]
+    ids_addr, vals_addr = rt.argmax_result()
+    torch.cuda.synchronize()
+
+    def enqueue_pass() -> None:
+        for name, t, rows, cols in tensors[:-1]:
+            rt.qmv(name, f"x{cols}", f"y{rows}", m)
+        name, t, rows, cols = tensors[-1]
+        rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
+
+    # single GPU: the whole pass is one CUDA graph; multi GPU: kernels on the runtime's stream, gathers after each
+    graph = None
+    if world == 1:
+        enqueue_pass()  # sets the kernels' attributes outside of capture
+        rt.synchronize()
+        rt.capture_begin()
+        enqueue_pass()
+        graph = rt.capture_end()
+
+    def device_pass() -> None:
+        if world == 1:
+            rt.graph_launch(graph)
+            return
+        with torch.cuda.stream(stream):
+            for name, t, rows, cols in tensors[:-1]:
+                rt.qmv(name, f"x{cols}", f"y{rows}", m)
+                dist.all_gather(gathered[rows], y_local[rows])
+            name, t, rows, cols = tensors[-1]
+            rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
+            dist.all_gather(gathered[rows], y_local[rows])
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps: int) -> float:
+        """ms per step: CUDA events on the launching stream, barrier + synchronize on both sides, max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            tmax = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            ms = float(tmax.item())
+        return ms
+
+    def e2e_step() -> None:
+        with torch.cuda.stream(stream):
+            for w in widths:
+                dev_x[w].copy_(host_x[w].view(-1), non_blocking=True)
+        device_pass()
+        ids, vals = rt.argmax_fetch(m, with_values=True)
+        if world > 1:  # global argmax: all-gather of (value, index) pairs, highest value wins, lowest index on ties
+            pair_local[:m] = torch.tensor(vals, device=dev)
+            pair_local[8 : 8 + m] = torch.tensor([float(i) for i in ids], device=dev)
+            dist.all_gather(pair_all, pair_local)
+
+    # -- warm-up, then the timed regions
+    for _ in range(max(3, args.warmup)):
+        device_pass()
+    launches_before = rt.launch_count()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(device_pass, args.steps)
+    launches = rt.launch_count() - launches_before
+    e2e_ms = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    # -- roofline of the dominant kernel: the Q3_K gate/up matvec alone over the model's distinct tensors
+    dom = [(n, t, r, c) for n, t, r, c in tensors if t is T.Q3_K]
+    d_rows = local_rows[dom[0][0]][1] - local_rows[dom[0][0]][0]
+
+    def dominant() -> None:
+        for name, t, rows, cols in dom:
+            rt.qmv(name, f"x{cols}", f"y{rows}", m)
+
+    dominant()
+    dom_ms = timed(dominant, max(2, args.steps // 2)) / len(dom)
+    alg_bytes = d_rows * (dom[0][3] // 256) * 110 + 4 * m * dom[0][3] + 4 * m * d_rows
+    peak, peak_kind = measured_peak_gbs()
+    achieved = alg_bytes / (dom_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        value = weight_bytes_total / (ms * 1e-3) / 1e9
+        e2e_value = weight_bytes_total / (e2e_ms * 1e-3) / 1e9
+        h2d = sum(4 * m * w for w in widths)
+        cpu = cpu_baseline(m, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"synthetic-27B decode pass, M={m}: 64 x (Q6_K q/k/v/o, Q3_K gate/up, Q4_K down) + Q6_K LM head 151936x5120 "
+                                   f"with fused argmax; {weight_bytes_total} weight bytes resident in HBM", "activation_rows": m,
+                       "launches_per_pass": len(tensors), "l2": "pass is ~100x larger than L2 (no flush needed)",
+                       "parallelism": "single GPU, one CUDA graph per pass" if world == 1 else f"output rows sharded over {world} GPUs, NCCL all-gather per matvec"},
+            "tokens_per_s": m / (ms * 1e-3), "pct_of_8TBs": 100.0 * value / 8000.0 / world,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * m,
+                    "tokens_per_s": m / (e2e_ms * 1e-3)},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": f"qmv_kernel<Q3_K, M={m}> {d_rows}x{dom[0][3]}",
+                         "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": dom_ms * 1e3, "peak_source": f"of {peak_kind}"},
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    rt.close()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--m", type=int, default=4, help="activation rows per pass (1..8)")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline leg (0 = skip)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

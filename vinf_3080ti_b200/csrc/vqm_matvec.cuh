@@ -224,7 +224,7 @@ struct Step<kQ4_K, M, RW> {
     // Scale table of the warp: for each (row, block, pair of groups) {dl, dl'/16, -ml, -ml'}, 16 bytes.  The
     // pairs with even and odd index live in two halves of the table so that consecutive lanes of the scale
     // pass store to consecutive 16-byte slots (no bank conflicts).
-    static constexpr int kHalf = RW * 4 * 32;
+    static constexpr int kHalf = RW * 4 * 32 + 32;  // + 32: the two halves start 8 banks apart
     static constexpr int kScratch = 2 * kHalf;
 
     // Rows of the chunk that do not exist are decoded from whatever the slot holds and thrown away by the
@@ -293,6 +293,149 @@ struct Step<kQ4_K, M, RW> {
         __syncwarp();  // the scratch table is rewritten by the next step
     }
 };
+
+// Q6_K and Q3_K share a block geometry: weight e = 128h + 32q + l (h: half, q: quarter, l < 32) takes its low bits from
+// byte 32h + l of a 64-byte plane (Q6_K: two planes of nibbles, Q3_K: one plane of 2-bit fields) and its high bits
+// from a second plane indexed by l, and weights 16k..16k+15 share sub-scale k = 8h + 2q + (l >> 4)
+// (engine/csrc/common/qwen_quant.cuh:182-190,199-210).  Neither carries a minimum, so
+//     sum_i dl q_i x_i = dl * sum_i q_i x_i      with q the raw field minus a constant (32 / 4).
+//   scale pass : lane -> (row, block, 4 sub-scales): integer sub-scale -> float, times d, stored so that a dot-pass
+//                lane finds the sub-scales of its four quarters in one 16-byte slot.
+//   dot pass   : lane -> (block, half h, 4 consecutive l = 4j..4j+3): one word of each plane gives 16 weights, 4 per
+//                quarter, at columns 128h + 32q + 4j.  Eight lanes read 128 contiguous bytes of activations.
+//                Blocks are only 2-byte aligned, so plane words are fetched with aligned loads + a funnel shift;
+//                a pass takes the blocks of equal parity, which have the same alignment in every lane.
+template <int TYPE>
+struct QuarterFormat;
+
+template <>
+struct QuarterFormat<kQ6_K> {
+    static constexpr int kBlockBytes = 210;
+    static constexpr float kBias = 32.0f;       // field - 32
+    static constexpr float kScaleBias = 128.0f;  // int8 sub-scale, read as (byte ^ 0x80) - 128
+    struct Words {
+        uint32_t ql0, ql1, qh;
+    };
+    static __device__ __forceinline__ Words load(const uint8_t *bp, int h, int j) {
+        return Words{ld32<2>(bp + 64 * h + 4 * j), ld32<2>(bp + 64 * h + 32 + 4 * j), ld32<2>(bp + 128 + 32 * h + 4 * j)};
+    }
+    // bytes = fields of quarter Q (4 weights), still carrying the bias
+    template <int Q>
+    static __device__ __forceinline__ uint32_t quarter(const Words &w, int) {
+        const uint32_t ql = (Q & 1) ? w.ql1 : w.ql0;
+        const uint32_t lo = (Q >= 2 ? (ql >> 4) : ql) & 0x0F0F0F0Fu;
+        const uint32_t hi = Q == 0 ? (w.qh << 4) : Q == 1 ? (w.qh << 2) : Q == 2 ? w.qh : (w.qh >> 2);
+        return lo | (hi & 0x30303030u);
+    }
+    // four sub-scales 4c..4c+3 as biased bytes, and d
+    static __device__ __forceinline__ uint32_t scale_word(const uint8_t *bp, int c, float *d) {
+        *d = half_bits_to_float(ld16(bp + 208));
+        return ld32<2>(bp + 192 + 4 * c) ^ 0x80808080u;
+    }
+};
+
+template <>
+struct QuarterFormat<kQ3_K> {
+    static constexpr int kBlockBytes = 110;
+    static constexpr float kBias = 4.0f;        // (low2 | high << 2) - 4
+    static constexpr float kScaleBias = 32.0f;  // 6-bit sub-scale - 32
+    struct Words {
+        uint32_t qs, hm;
+    };
+    static __device__ __forceinline__ Words load(const uint8_t *bp, int h, int j) {
+        return Words{ld32<2>(bp + 32 + 32 * h + 4 * j), ld32<2>(bp + 4 * j) >> (4 * h)};
+    }
+    template <int Q>
+    static __device__ __forceinline__ uint32_t quarter(const Words &w, int) {
+        const uint32_t lo = (Q == 0 ? w.qs : (w.qs >> (2 * Q))) & 0x03030303u;
+        const uint32_t hb = Q == 0 ? (w.hm << 2) : Q == 1 ? (w.hm << 1) : Q == 2 ? w.hm : (w.hm >> 1);
+        return lo | (hb & 0x04040404u);
+    }
+    static __device__ __forceinline__ uint32_t scale_word(const uint8_t *bp, int c, float *d) {
+        *d = half_bits_to_float(ld16(bp + 108));
+        // sub-scale k: low nibble from byte k % 8 (>> 4 for k >= 8), high 2 bits from byte 8 + k % 4 (>> 2 (k / 4))
+        const uint32_t wl = ld32<2>(bp + 96 + 4 * (c & 1)), w2 = ld32<2>(bp + 104);
+        const uint32_t lo = (wl >> (4 * (c >> 1))) & 0x0F0F0F0Fu;
+        const uint32_t hi = static_cast<uint32_t>((static_cast<unsigned long long>(w2) << 4) >> (2 * c)) & 0x30303030u;
+        return lo | hi;
+    }
+};
+
+template <int TYPE, int M, int RW>
+struct QuarterStep {
+    using F = QuarterFormat<TYPE>;
+    static constexpr int kEntry = 64;  // per (row, block): 16 sub-scales x d, as [h][l >> 4][quarter]
+    static constexpr int kScratch = RW * 4 * kEntry;
+
+    static __device__ __forceinline__ void run(const uint8_t *stage, uint32_t d0, uint32_t rb16, uint8_t *scratch, const uint8_t *,
+                                               const float *xs, int cols, int, f32x2 (&acc)[RW][M], int lane) {
+        constexpr int SLOT = slot_bytes(TYPE), BB = F::kBlockBytes;
+        const int nblk = cols >> 8;
+        // ---- scale pass: task -> (row, block, scale word c)
+        {
+            const f32x2 neg_magic = pack2(-(8388608.0f + F::kScaleBias), -(8388608.0f + F::kScaleBias));
+#pragma unroll
+            for (int task0 = 0; task0 < 16 * RW; task0 += 32) {
+                const int task = task0 + lane, r = task >> 4, blk = (task >> 2) & 3, c = task & 3;
+                if (16 * RW % 32 == 0 || task < 16 * RW) {
+                    const uint8_t *bp = stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB;
+                    float d;
+                    const uint32_t sw = F::scale_word(bp, c, &d);
+                    const f32x2 dd = pack2(d, d);
+                    // sub-scale k = 4c + i belongs to half k >> 3, quarter (k >> 1) & 3, l >> 4 = k & 1
+                    float *dst = reinterpret_cast<float *>(scratch + (r * 4 + blk) * kEntry) + (c >> 1) * 8 + 2 * (c & 1);
+                    *reinterpret_cast<f32x2 *>(dst) = mul2(bytes_to_pair<0, 2>(sw, neg_magic), dd);      // l < 16: quarters 2(c&1), +1
+                    *reinterpret_cast<f32x2 *>(dst + 4) = mul2(bytes_to_pair<1, 3>(sw, neg_magic), dd);  // l >= 16
+                }
+            }
+        }
+        __syncwarp();
+        // ---- dot pass
+        const f32x2 neg_magic = pack2(-(8388608.0f + F::kBias), -(8388608.0f + F::kBias));
+        const int bsel = lane >> 4, h = (lane >> 3) & 1, j = lane & 7;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const int blk = s + 2 * bsel;
+            if (blk < nblk) {
+                typename F::Words w[RW];
+                float4 dl[RW];
+#pragma unroll
+                for (int r = 0; r < RW; ++r) {
+                    w[r] = F::load(stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB, h, j);
+                    dl[r] = *reinterpret_cast<const float4 *>(scratch + (r * 4 + blk) * kEntry + (h * 2 + (j >> 2)) * 16);
+                }
+                const float *xq = xs + blk * 256 + h * 128 + 4 * j;
+                quarter_dot<0>(w, dl, xq, neg_magic, acc);
+                quarter_dot<1>(w, dl, xq, neg_magic, acc);
+                quarter_dot<2>(w, dl, xq, neg_magic, acc);
+                quarter_dot<3>(w, dl, xq, neg_magic, acc);
+            }
+        }
+        __syncwarp();  // the scratch table is rewritten by the next step
+    }
+
+    template <int Q>
+    static __device__ __forceinline__ void quarter_dot(const typename F::Words (&w)[RW], const float4 (&dl)[RW], const float *xq,
+                                                       f32x2 neg_magic, f32x2 (&acc)[RW][M]) {
+        X4 x[M];
+#pragma unroll
+        for (int t = 0; t < M; ++t) x[t] = lds_x4(xq + t * kSegCols + Q * 32);
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            const uint32_t q = F::template quarter<Q>(w[r], 0);
+            const f32x2 q01 = bytes_to_pair<0, 1>(q, neg_magic), q23 = bytes_to_pair<2, 3>(q, neg_magic);
+            const float d = Q == 0 ? dl[r].x : Q == 1 ? dl[r].y : Q == 2 ? dl[r].z : dl[r].w;
+            const f32x2 d2 = pack2(d, d);
+#pragma unroll
+            for (int t = 0; t < M; ++t) acc[r][t] = fma2(d2, fma2(q23, x[t].p23, mul2(q01, x[t].p01)), acc[r][t]);
+        }
+    }
+};
+
+template <int M, int RW>
+struct Step<kQ6_K, M, RW> : QuarterStep<kQ6_K, M, RW> {};
+template <int M, int RW>
+struct Step<kQ3_K, M, RW> : QuarterStep<kQ3_K, M, RW> {};
 
 // ---- the kernel ------------------------------------------------------------------------------------------
 

@@ -10,36 +10,70 @@
 namespace vqm {
 namespace {
 
-// Rows a warp takes per chunk: 8 for one or two activation rows (more independent work per staged
-// activation load), 4 beyond that (registers), 2 where eight-row stages of a wide type do not fit.
-template <int M>
-constexpr int rows_per_chunk() {
-    constexpr int want = M <= 2 ? 8 : 4;
-    return matvec_smem_bytes_for<VQM_TYPE, want, M>() <= 100 * 1024 ? want
-         : matvec_smem_bytes_for<VQM_TYPE, want / 2, M>() <= 200 * 1024 ? want / 2 : want / 4;
-}
+// One kernel per (activation rows M, rows per chunk RW).  A warp always decodes RW rows per chunk (rows that do not
+// exist are computed and dropped), so RW is chosen per launch: the smallest height that covers a warp's share of
+// the rows, up to 8 for one or two activation rows and 4 beyond that (registers, and RW * M <= 32 outputs per warp).
+template <int M, int RW>
+struct Variant {
+    static constexpr size_t kSmem = matvec_smem_bytes_for<VQM_TYPE, RW, M>();
+    static constexpr bool kFits = kSmem <= 200 * 1024 && RW * M <= 32;
+
+    // blocks per SM (cached; one device per process), 0 if the variant cannot run
+    static int blocks_per_sm() {
+        static int cached = -1;
+        if (cached >= 0) return cached;
+        cached = 0;
+        if constexpr (kFits) {
+            if (cudaFuncSetAttribute(qmv_kernel<VQM_TYPE, M, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kSmem)) == cudaSuccess) {
+                int n = 0;
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, qmv_kernel<VQM_TYPE, M, RW>, kWarps * 32, kSmem) == cudaSuccess)
+                    cached = n;
+            }
+            (void)cudaGetLastError();
+        }
+        return cached;
+    }
+
+    // rows each warp would get in a one-wave launch (rounded up), or 0 if the variant cannot run
+    static int rows_per_warp(int rows, int sm_count) {
+        const int b = blocks_per_sm();
+        if (b == 0) return 0;
+        const int warps = grid_for(rows, sm_count, b) * kWarps;
+        return (rows + warps - 1) / warps;
+    }
+
+    static int grid_for(int rows, int sm_count, int b) {
+        // one wave; a short tensor gets fewer blocks so that every warp still has a row
+        const int grid = sm_count * b, want = (rows + kWarps - 1) / kWarps;
+        return grid < want ? grid : want;
+    }
+
+    static cudaError_t launch(const MatvecArgs &a, int sm_count, cudaStream_t stream, int *grid_out) {
+        if constexpr (kFits) {
+            const int grid = grid_for(a.rows, sm_count, blocks_per_sm());
+            if (grid_out != nullptr) *grid_out = grid;
+            qmv_kernel<VQM_TYPE, M, RW><<<grid, kWarps * 32, kSmem, stream>>>(a);
+            return cudaGetLastError();
+        } else {
+            return cudaErrorInvalidConfiguration;
+        }
+    }
+};
 
 template <int M>
 cudaError_t launch_one(const MatvecArgs &a, int sm_count, cudaStream_t stream, int *grid_out) {
-    constexpr int RW = rows_per_chunk<M>();
-    constexpr size_t smem = matvec_smem_bytes_for<VQM_TYPE, RW, M>();
-    static int blocks_per_sm = 0;  // one device per process
-    if (blocks_per_sm == 0) {
-        cudaError_t err = cudaFuncSetAttribute(qmv_kernel<VQM_TYPE, M, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(smem));
-        if (err != cudaSuccess) return err;
-        int n = 0;
-        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, qmv_kernel<VQM_TYPE, M, RW>, kWarps * 32, smem);
-        if (err != cudaSuccess) return err;
-        blocks_per_sm = n > 0 ? n : 1;
+    constexpr int kMaxRw = M <= 2 ? 8 : 4;
+    // smallest RW that holds a warp's share; the tallest that can run if the share needs several chunks anyway
+    if (const int n = Variant<M, 1>::rows_per_warp(a.rows, sm_count); n > 0 && n <= 1) return Variant<M, 1>::launch(a, sm_count, stream, grid_out);
+    if (const int n = Variant<M, 2>::rows_per_warp(a.rows, sm_count); n > 0 && n <= 2) return Variant<M, 2>::launch(a, sm_count, stream, grid_out);
+    if (const int n = Variant<M, 4>::rows_per_warp(a.rows, sm_count); n > 0 && (n <= 4 || kMaxRw == 4)) return Variant<M, 4>::launch(a, sm_count, stream, grid_out);
+    if constexpr (kMaxRw == 8) {
+        if (Variant<M, 8>::blocks_per_sm() > 0) return Variant<M, 8>::launch(a, sm_count, stream, grid_out);
     }
-    // one wave; a short tensor gets fewer blocks so that every warp still has a row
-    int grid = sm_count * blocks_per_sm;
-    const int want = (a.rows + kWarps - 1) / kWarps;
-    if (grid > want) grid = want;
-    if (grid_out != nullptr) *grid_out = grid;
-    qmv_kernel<VQM_TYPE, M, RW><<<grid, kWarps * 32, smem, stream>>>(a);
-    return cudaGetLastError();
+    if (Variant<M, 4>::blocks_per_sm() > 0) return Variant<M, 4>::launch(a, sm_count, stream, grid_out);
+    if (Variant<M, 2>::blocks_per_sm() > 0) return Variant<M, 2>::launch(a, sm_count, stream, grid_out);
+    return Variant<M, 1>::launch(a, sm_count, stream, grid_out);
 }
 
 }  // namespace
