@@ -22,6 +22,7 @@ struct MatvecArgs {
     int rows, cols;
     long long row_bytes;
     int row_base;            // added to row numbers reported by the argmax (row-sharded weights)
+    int overlap_launch;      // host only: launch with programmatic stream serialization (see qmv_kernel)
 };
 
 enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1 };

@@ -227,10 +227,9 @@ struct Step<kQ4_K, M, RW> {
     static constexpr int kHalf = RW * 4 * 32 + 32;  // + 32: the two halves start 8 banks apart
     static constexpr int kScratch = 2 * kHalf;
 
-    // Rows of the chunk that do not exist are decoded from whatever the slot holds and thrown away by the
-    // caller: one straight-line code path is cheaper than predicating every row.
+    // Rows of the chunk that do not exist are skipped with warp-uniform branches.
     static __device__ __forceinline__ void run(const uint8_t *stage, uint32_t, uint32_t, uint8_t *scratch, const uint8_t *,
-                                               const float *xs, int cols, int, f32x2 (&acc)[RW][M], int lane) {
+                                               const float *xs, int cols, int nrows, f32x2 (&acc)[RW][M], int lane) {
         constexpr int SLOT = slot_bytes(kQ4_K);
         const int nblk = cols >> 8;
         const f32x2 neg_magic = pack2(-8388608.0f, -8388608.0f);
@@ -238,7 +237,7 @@ struct Step<kQ4_K, M, RW> {
 #pragma unroll
         for (int r0 = 0; r0 < RW; r0 += 4) {
             const int r = r0 + (lane >> 3), blk = (lane >> 1) & 3, hh = lane & 1;
-            if (RW >= 4 || r < RW) {
+            if (r < nrows) {
                 const uint4 h = *reinterpret_cast<const uint4 *>(stage + r * SLOT + blk * 144);
                 const float d = half_bits_to_float(h.x & 0xFFFFu), ndmin = -half_bits_to_float(h.x >> 16);
                 // four 6-bit fields at a time (engine/csrc/common/qwen_quant.cuh:78-86)
@@ -273,6 +272,7 @@ struct Step<kQ4_K, M, RW> {
                 }
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
+                    if (r >= nrows) break;
                     const uint32_t w = *reinterpret_cast<const uint32_t *>(stage + r * SLOT + blk * 144 + 16 + 4 * lane);
                     const uint32_t lo = w & 0x0F0F0F0Fu, hi = w & 0xF0F0F0F0u;
                     const f32x2 a01 = bytes_to_pair<0, 1>(lo, neg_magic), a23 = bytes_to_pair<2, 3>(lo, neg_magic);
@@ -368,7 +368,7 @@ struct QuarterStep {
     static constexpr int kScratch = RW * 4 * kEntry;
 
     static __device__ __forceinline__ void run(const uint8_t *stage, uint32_t d0, uint32_t rb16, uint8_t *scratch, const uint8_t *,
-                                               const float *xs, int cols, int, f32x2 (&acc)[RW][M], int lane) {
+                                               const float *xs, int cols, int nrows, f32x2 (&acc)[RW][M], int lane) {
         constexpr int SLOT = slot_bytes(TYPE), BB = F::kBlockBytes;
         const int nblk = cols >> 8;
         // ---- scale pass: task -> (row, block, scale word c)
@@ -377,7 +377,7 @@ struct QuarterStep {
 #pragma unroll
             for (int task0 = 0; task0 < 16 * RW; task0 += 32) {
                 const int task = task0 + lane, r = task >> 4, blk = (task >> 2) & 3, c = task & 3;
-                if (16 * RW % 32 == 0 || task < 16 * RW) {
+                if (r < nrows) {
                     const uint8_t *bp = stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB;
                     float d;
                     const uint32_t sw = F::scale_word(bp, c, &d);
@@ -401,14 +401,15 @@ struct QuarterStep {
                 float4 dl[RW];
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
+                    if (r >= nrows) break;
                     w[r] = F::load(stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB, h, j);
                     dl[r] = *reinterpret_cast<const float4 *>(scratch + (r * 4 + blk) * kEntry + (h * 2 + (j >> 2)) * 16);
                 }
                 const float *xq = xs + blk * 256 + h * 128 + 4 * j;
-                quarter_dot<0>(w, dl, xq, neg_magic, acc);
-                quarter_dot<1>(w, dl, xq, neg_magic, acc);
-                quarter_dot<2>(w, dl, xq, neg_magic, acc);
-                quarter_dot<3>(w, dl, xq, neg_magic, acc);
+                quarter_dot<0>(w, dl, xq, neg_magic, nrows, acc);
+                quarter_dot<1>(w, dl, xq, neg_magic, nrows, acc);
+                quarter_dot<2>(w, dl, xq, neg_magic, nrows, acc);
+                quarter_dot<3>(w, dl, xq, neg_magic, nrows, acc);
             }
         }
         __syncwarp();  // the scratch table is rewritten by the next step
@@ -416,12 +417,13 @@ struct QuarterStep {
 
     template <int Q>
     static __device__ __forceinline__ void quarter_dot(const typename F::Words (&w)[RW], const float4 (&dl)[RW], const float *xq,
-                                                       f32x2 neg_magic, f32x2 (&acc)[RW][M]) {
+                                                       f32x2 neg_magic, int nrows, f32x2 (&acc)[RW][M]) {
         X4 x[M];
 #pragma unroll
         for (int t = 0; t < M; ++t) x[t] = lds_x4(xq + t * kSegCols + Q * 32);
 #pragma unroll
         for (int r = 0; r < RW; ++r) {
+            if (r >= nrows) break;
             const uint32_t q = F::template quarter<Q>(w[r], 0);
             const f32x2 q01 = bytes_to_pair<0, 1>(q, neg_magic), q23 = bytes_to_pair<2, 3>(q, neg_magic);
             const float d = Q == 0 ? dl[r].x : Q == 1 ? dl[r].y : Q == 2 ? dl[r].z : dl[r].w;
@@ -533,12 +535,18 @@ __global__ void __launch_bounds__(kWarps * 32, (M <= 4 ? 2 : 1)) qmv_kernel(cons
         }
     };
 
+    // The weights never depend on an earlier kernel, so their first copies go out at once; everything that reads the
+    // activations or writes outputs comes after griddepcontrol.wait.  With programmatic dependent launch this block
+    // may have started while the previous kernel of the stream was still draining, which hides the launch latency
+    // and the first-byte latency of the weight stream (without that launch attribute both instructions are no-ops).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    int issued = 0;
+    for (; issued < S && issued < n_steps; ++issued) issue_w();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
         const int n = n_steps < XS ? n_steps : XS;
         for (int s = 0; s < n; ++s) issue_x(s, s % n_seg);
     }
-    int issued = 0;
-    for (; issued < S && issued < n_steps; ++issued) issue_w();
 
     if constexpr (TABLE > 0) {
         if constexpr (grid_is_codebook(TYPE)) {

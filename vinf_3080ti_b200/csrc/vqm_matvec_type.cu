@@ -53,8 +53,17 @@ struct Variant {
         if constexpr (kFits) {
             const int grid = grid_for(a.rows, sm_count, blocks_per_sm());
             if (grid_out != nullptr) *grid_out = grid;
-            qmv_kernel<VQM_TYPE, M, RW><<<grid, kWarps * 32, kSmem, stream>>>(a);
-            return cudaGetLastError();
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(grid);
+            cfg.blockDim = dim3(kWarps * 32);
+            cfg.dynamicSmemBytes = kSmem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = a.overlap_launch ? 1 : 0;
+            return cudaLaunchKernelEx(&cfg, qmv_kernel<VQM_TYPE, M, RW>, a);
         } else {
             return cudaErrorInvalidConfiguration;
         }

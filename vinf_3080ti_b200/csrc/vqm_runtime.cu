@@ -7,6 +7,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <unordered_map>
@@ -80,6 +81,7 @@ struct vqm_runtime {
     float *scratch_x = nullptr, *scratch_y = nullptr;
     size_t scratch_x_n = 0, scratch_y_n = 0;
     int gemm_min_rows = 0;
+    int overlap_launch = 1;  // programmatic dependent launch of consecutive matvecs (VINF_B200_NO_PDL=1 turns it off)
     bool capturing = false;
     uint64_t launches = 0, capture_launches = 0;
     std::vector<Graph> graphs;
@@ -178,6 +180,7 @@ int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int
     a.rows = t.rows;
     a.cols = t.cols;
     a.row_bytes = static_cast<long long>(t.row_bytes);
+    a.overlap_launch = rt->overlap_launch;
     if (with_argmax) {
         a.part_val = rt->part_val;
         a.part_idx = rt->part_idx;
@@ -232,6 +235,7 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
         return rc;
     }
     rt->done_counter = rt->status + 16;
+    if (const char *e = getenv("VINF_B200_NO_PDL"); e != nullptr && e[0] == '1') rt->overlap_launch = 0;
     if (iq3s_grid != nullptr) {
         const int rc = vqm_set_codebook(rt, "iq3s_grid", iq3s_grid, nbytes);
         if (rc != VQM_OK) {
