@@ -1,0 +1,248 @@
+// Tuned step decoders for Q4_K, Q6_K and Q3_K (the types of the 27B layer set).  See vqm_steps.cuh for the interface.
+//
+// Common idea: the per-weight work is "raw field -> float" (one byte permute per weight, one packed add per two), one
+// packed multiply by the group scale dl (exact: the product has at most 23 significant bits, it is the dequantised
+// weight without its minimum) and one FMA per activation row.  The minimum of the types that carry one is taken out
+// of the sum:  sum_i (dl q_i - ml) x_i = sum_i (dl q_i) x_i - ml * sum_i x_i.  Sub-scales are decoded once per step
+// by a scale pass (word-wide mask arithmetic, four sub-scales per lane) into a per-warp table of (dl, dl) pairs.
+// The sequence of operations per output does not depend on the number of activation rows.
+#pragma once
+
+#include "vqm_steps.cuh"
+
+namespace vqm {
+
+// ---- Q4_K --------------------------------------------------------------------------------------------------
+// Block (144 B, always 16-byte aligned): d, dmin (f16) | 12 bytes of 6-bit scales and mins | 128 bytes of nibbles;
+// bytes 32p..32p+31 hold group 2p in their low and group 2p+1 in their high nibbles
+// (engine/csrc/common/qwen_quant.cuh:165-175).
+//   scale pass : lane -> (row, block, groups 4hh..4hh+3).  Per (row, block, pair of groups p) it leaves
+//                {dl, dl, dl'/16, dl'/16} and {-ml, -ml', 0, 0} (/16 because the high nibbles stay in place) in four
+//                "piece" arrays indexed by lane, so that its stores and the dot pass's loads are conflict-free.
+//   dot pass   : one block at a time, lane i -> 32-bit word i of the nibbles: 4 weights of group 2p (columns
+//                64p + 4(i%8) ..) and 4 of group 2p+1 (32 columns further), p = i / 8.  Eight lanes read 128
+//                contiguous bytes of activations per load, so the shared-memory reads are conflict-free.
+template <int M, int RW>
+struct Step<kQ4_K, M, RW> {
+    // piece 2w: scales, piece 2w + 1: mins of pair p = 2hh + w; slot (row * 4 + block) * 2 + hh of 16 bytes in each piece
+    static constexpr int kPiece = RW * 4 * 2 * 16 + 32;  // + 32: consecutive pieces start 8 banks apart
+    static constexpr int kScratch = 4 * kPiece;
+
+    template <int NR>
+    struct Pass {
+        static __device__ __forceinline__ void go(uint32_t stage, uint32_t scratch, uint32_t xs, int nblk, f32x2 (&acc)[RW][M], int lane) {
+            constexpr int SLOT = slot_bytes(kQ4_K);
+            const f32x2 neg_magic = pack2(-8388608.0f, -8388608.0f);
+            // ---- scale pass
+#pragma unroll
+            for (int r0 = 0; r0 < NR; r0 += 4) {
+                const int r = r0 + (lane >> 3), blk = (lane >> 1) & 3, hh = lane & 1;
+                if (r < NR) {
+                    const uint4 h = lds128u(stage + r * SLOT + blk * 144);
+                    const float d = half_bits_to_float(h.x & 0xFFFFu), ndmin = -half_bits_to_float(h.x >> 16);
+                    // four 6-bit fields at a time (engine/csrc/common/qwen_quant.cuh:78-86)
+                    const uint32_t scw = hh ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
+                    const uint32_t mnw = hh ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
+                    const f32x2 dlo = pack2(d, d), dhi = pack2(d * 0.0625f, d * 0.0625f), mm = pack2(ndmin, ndmin);
+                    const uint32_t dst = scratch + ((r * 4 + blk) * 2 + hh) * 16;
+                    sts128(dst, mul2(bytes_to_pair<0, 0>(scw, neg_magic), dlo), mul2(bytes_to_pair<1, 1>(scw, neg_magic), dhi));
+                    sts128(dst + kPiece, mul2(bytes_to_pair<0, 1>(mnw, neg_magic), mm), 0ull);
+                    sts128(dst + 2 * kPiece, mul2(bytes_to_pair<2, 2>(scw, neg_magic), dlo), mul2(bytes_to_pair<3, 3>(scw, neg_magic), dhi));
+                    sts128(dst + 3 * kPiece, mul2(bytes_to_pair<2, 3>(mnw, neg_magic), mm), 0ull);
+                }
+            }
+            __syncwarp();
+            // ---- dot pass
+            const int p = lane >> 3;
+            const uint32_t xl = xs + (p * 64 + 4 * (lane & 7)) * 4;
+            const uint32_t el = scratch + (p & 1) * 2 * kPiece + (p >> 1) * 16;
+            const uint32_t wl = stage + 16 + 4 * lane;
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+                if (blk < nblk) {
+                    X4 xa[M], xb[M];
+                    f32x2 sx[M];
+#pragma unroll
+                    for (int t = 0; t < M; ++t) {
+                        xa[t] = lds_x4(xl + (t * kSegCols + blk * 256) * 4);
+                        xb[t] = lds_x4(xl + (t * kSegCols + blk * 256 + 32) * 4);
+                        sx[t] = pack2(sum_x4(xa[t]), sum_x4(xb[t]));
+                    }
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) {
+                        const uint32_t w = lds32(wl + r * SLOT + blk * 144);
+                        const uint32_t lo = w & 0x0F0F0F0Fu, hi = w & 0xF0F0F0F0u;
+                        f32x2 a01 = bytes_to_pair<0, 1>(lo, neg_magic), a23 = bytes_to_pair<2, 3>(lo, neg_magic);
+                        f32x2 b01 = bytes_to_pair<0, 1>(hi, neg_magic), b23 = bytes_to_pair<2, 3>(hi, neg_magic);
+                        const ulonglong2 dl = lds128(el + (r * 4 + blk) * 32);           // (dl, dl), (dl'/16, dl'/16)
+                        const f32x2 nml = lds64(el + (r * 4 + blk) * 32 + kPiece);      // (-ml, -ml')
+                        // exact products (at most 21 significant bits): the dequantised weights without their minimum
+                        a01 = mul2(a01, dl.x);
+                        a23 = mul2(a23, dl.x);
+                        b01 = mul2(b01, dl.y);
+                        b23 = mul2(b23, dl.y);
+#pragma unroll
+                        for (int t = 0; t < M; ++t)
+                            acc[r][t] = fma2(nml, sx[t], fma2(b23, xb[t].p23, fma2(b01, xb[t].p01,
+                                        fma2(a23, xa[t].p23, fma2(a01, xa[t].p01, acc[r][t])))));
+                    }
+                }
+            }
+            __syncwarp();  // the scratch table is rewritten by the next step
+        }
+    };
+
+    static __device__ __forceinline__ void run(uint32_t stage, uint32_t, uint32_t, uint32_t scratch, uint32_t, uint32_t xs, int cols,
+                                               int nrows, f32x2 (&acc)[RW][M], int lane) {
+        dispatch_rows<Pass, RW>(nrows, stage, scratch, xs, cols >> 8, acc, lane);
+    }
+};
+
+// ---- Q6_K and Q3_K ---------------------------------------------------------------------------------------------
+// Both share a block geometry: weight e = 128h + 32q + l (h: half, q: quarter, l < 32) takes its low bits from byte
+// 32h + l of a 64-byte plane (Q6_K: two planes of nibbles, Q3_K: one plane of 2-bit fields) and its high bits from a
+// second plane indexed by l, and weights 16k..16k+15 share sub-scale k = 8h + 2q + (l >> 4)
+// (engine/csrc/common/qwen_quant.cuh:182-190,199-210).  Neither carries a minimum.
+//   scale pass : lane -> (row, block, 4 sub-scales): integer sub-scale -> float, times d, stored as (dl, dl) pairs so
+//                that a dot-pass lane finds the sub-scales of its four quarters in one 32-byte slot [h][l >> 4][q].
+//   dot pass   : lane -> (block, half h, 4 consecutive l = 4j..4j+3): one word of each plane gives 16 weights, 4 per
+//                quarter, at columns 128h + 32q + 4j.  Eight lanes read 128 contiguous bytes of activations.
+//                Blocks are only 2-byte aligned, so plane words are fetched with aligned loads + a funnel shift.
+template <int TYPE>
+struct QuarterFormat;
+
+template <>
+struct QuarterFormat<kQ6_K> {
+    static constexpr int kBlockBytes = 210;
+    static constexpr float kBias = 32.0f;       // field - 32
+    static constexpr float kScaleBias = 128.0f;  // int8 sub-scale, read as (byte ^ 0x80) - 128
+    struct Words {
+        uint32_t ql0, ql1, qh;
+    };
+    static __device__ __forceinline__ Words load(uint32_t bp, int h, int j) {
+        return Words{lds32_a2(bp + 64 * h + 4 * j), lds32_a2(bp + 64 * h + 32 + 4 * j), lds32_a2(bp + 128 + 32 * h + 4 * j)};
+    }
+    // bytes = fields of quarter Q (4 weights), still carrying the bias
+    template <int Q>
+    static __device__ __forceinline__ uint32_t quarter(const Words &w) {
+        const uint32_t ql = (Q & 1) ? w.ql1 : w.ql0;
+        const uint32_t lo = (Q >= 2 ? (ql >> 4) : ql) & 0x0F0F0F0Fu;
+        const uint32_t hi = Q == 0 ? (w.qh << 4) : Q == 1 ? (w.qh << 2) : Q == 2 ? w.qh : (w.qh >> 2);
+        return lo | (hi & 0x30303030u);
+    }
+    // four sub-scales 4c..4c+3 as biased bytes, and d
+    static __device__ __forceinline__ uint32_t scale_word(uint32_t bp, int c, float *d) {
+        *d = half_bits_to_float(lds16(bp + 208));
+        return lds32_a2(bp + 192 + 4 * c) ^ 0x80808080u;
+    }
+};
+
+template <>
+struct QuarterFormat<kQ3_K> {
+    static constexpr int kBlockBytes = 110;
+    static constexpr float kBias = 4.0f;        // (low2 | high << 2) - 4
+    static constexpr float kScaleBias = 32.0f;  // 6-bit sub-scale - 32
+    struct Words {
+        uint32_t qs, hm;
+    };
+    static __device__ __forceinline__ Words load(uint32_t bp, int h, int j) {
+        return Words{lds32_a2(bp + 32 + 32 * h + 4 * j), lds32_a2(bp + 4 * j) >> (4 * h)};
+    }
+    template <int Q>
+    static __device__ __forceinline__ uint32_t quarter(const Words &w) {
+        const uint32_t lo = (Q == 0 ? w.qs : (w.qs >> (2 * Q))) & 0x03030303u;
+        const uint32_t hb = Q == 0 ? (w.hm << 2) : Q == 1 ? (w.hm << 1) : Q == 2 ? w.hm : (w.hm >> 1);
+        return lo | (hb & 0x04040404u);
+    }
+    static __device__ __forceinline__ uint32_t scale_word(uint32_t bp, int c, float *d) {
+        *d = half_bits_to_float(lds16(bp + 108));
+        // sub-scale k: low nibble from byte k % 8 (>> 4 for k >= 8), high 2 bits from byte 8 + k % 4 (>> 2 (k / 4))
+        const uint32_t wl = lds32_a2(bp + 96 + 4 * (c & 1)), w2 = lds32_a2(bp + 104);
+        const uint32_t lo = (wl >> (4 * (c >> 1))) & 0x0F0F0F0Fu;
+        const uint32_t hi = static_cast<uint32_t>((static_cast<unsigned long long>(w2) << 4) >> (2 * c)) & 0x30303030u;
+        return lo | hi;
+    }
+};
+
+template <int TYPE, int M, int RW>
+struct QuarterStep {
+    using F = QuarterFormat<TYPE>;
+    static constexpr int kEntry = 128;  // per (row, block): 16 sub-scales x (dl, dl), as [h][l >> 4][quarter]
+    static constexpr int kScratch = RW * 4 * kEntry;
+
+    template <int NR>
+    struct Pass {
+        template <int Q>
+        static __device__ __forceinline__ void quarter_dot(const typename F::Words (&w)[NR], uint32_t el, uint32_t xq, f32x2 neg_magic,
+                                                           f32x2 (&acc)[RW][M]) {
+            X4 x[M];
+#pragma unroll
+            for (int t = 0; t < M; ++t) x[t] = lds_x4(xq + (t * kSegCols + Q * 32) * 4);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t q = F::template quarter<Q>(w[r]);
+                f32x2 q01 = bytes_to_pair<0, 1>(q, neg_magic), q23 = bytes_to_pair<2, 3>(q, neg_magic);
+                const f32x2 d2 = lds64(el + r * 4 * kEntry + Q * 8);
+                q01 = mul2(q01, d2);  // exact: the dequantised weights
+                q23 = mul2(q23, d2);
+#pragma unroll
+                for (int t = 0; t < M; ++t) acc[r][t] = fma2(q23, x[t].p23, fma2(q01, x[t].p01, acc[r][t]));
+            }
+        }
+
+        static __device__ __forceinline__ void go(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t scratch, uint32_t xs, int nblk,
+                                                  f32x2 (&acc)[RW][M], int lane) {
+            constexpr int SLOT = slot_bytes(TYPE), BB = F::kBlockBytes;
+            // ---- scale pass: task -> (row, block, scale word c)
+            {
+                const f32x2 neg_magic = pack2(-(8388608.0f + F::kScaleBias), -(8388608.0f + F::kScaleBias));
+#pragma unroll
+                for (int task0 = 0; task0 < 16 * NR; task0 += 32) {
+                    const int task = task0 + lane, r = task >> 4, blk = (task >> 2) & 3, c = task & 3;
+                    if (r < NR) {
+                        const uint32_t bp = stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB;
+                        float d;
+                        const uint32_t sw = F::scale_word(bp, c, &d);
+                        const f32x2 dd = pack2(d, d);
+                        // sub-scale k = 4c + i belongs to half k >> 3, quarter (k >> 1) & 3, l >> 4 = k & 1
+                        const uint32_t dst = scratch + (r * 4 + blk) * kEntry + (c >> 1) * 64 + (c & 1) * 16;
+                        sts128(dst, mul2(bytes_to_pair<0, 0>(sw, neg_magic), dd), mul2(bytes_to_pair<2, 2>(sw, neg_magic), dd));       // l < 16
+                        sts128(dst + 32, mul2(bytes_to_pair<1, 1>(sw, neg_magic), dd), mul2(bytes_to_pair<3, 3>(sw, neg_magic), dd));  // l >= 16
+                    }
+                }
+            }
+            __syncwarp();
+            // ---- dot pass: a pass takes blocks s and s + 2
+            const f32x2 neg_magic = pack2(-(8388608.0f + F::kBias), -(8388608.0f + F::kBias));
+            const int bsel = lane >> 4, h = (lane >> 3) & 1, j = lane & 7;
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                const int blk = s + 2 * bsel;
+                if (blk < nblk) {
+                    typename F::Words w[NR];
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) w[r] = F::load(stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB, h, j);
+                    const uint32_t el = scratch + blk * kEntry + (h * 2 + (j >> 2)) * 32;
+                    const uint32_t xq = xs + (blk * 256 + h * 128 + 4 * j) * 4;
+                    quarter_dot<0>(w, el, xq, neg_magic, acc);
+                    quarter_dot<1>(w, el, xq, neg_magic, acc);
+                    quarter_dot<2>(w, el, xq, neg_magic, acc);
+                    quarter_dot<3>(w, el, xq, neg_magic, acc);
+                }
+            }
+            __syncwarp();  // the scratch table is rewritten by the next step
+        }
+    };
+
+    static __device__ __forceinline__ void run(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t scratch, uint32_t, uint32_t xs,
+                                               int cols, int nrows, f32x2 (&acc)[RW][M], int lane) {
+        dispatch_rows<Pass, RW>(nrows, stage, d0, rb16, scratch, xs, cols >> 8, acc, lane);
+    }
+};
+
+template <int M, int RW>
+struct Step<kQ6_K, M, RW> : QuarterStep<kQ6_K, M, RW> {};
+template <int M, int RW>
+struct Step<kQ3_K, M, RW> : QuarterStep<kQ3_K, M, RW> {};
+
+}  // namespace vqm
