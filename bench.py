@@ -34,6 +34,7 @@ REPO = Path(__file__).resolve().parent
 sys.path.insert(0, str(REPO))
 
 from vinf_3080ti_b200.gguf_types import F16_FIELDS, TRAITS, GGUFTensorType as T  # noqa: E402
+from vinf_3080ti_b200.sharding import pick_best, shard_rows  # noqa: E402
 from vinf_3080ti_b200.synth import LAYER_SET, LM_HEAD, N_LAYERS, synthetic_activations, synthetic_blocks, tensor_bytes  # noqa: E402
 
 METRIC = "quant-matvec weight GB/s, synthetic-27B decode pass"
@@ -94,15 +95,6 @@ class ClockSampler:
         busy = [v for v in sm if v > 0.5 * max(sm)] if sm else []
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
-
-
-def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
-    """Contiguous slice [begin, end) of the output rows owned by `rank`; the start stays even so that the
-    slice of a 2-byte-aligned block format begins on a 4-byte boundary like the full tensor's rows."""
-    per = (rows // world) & ~1
-    begin = rank * per
-    end = rows if rank == world - 1 else begin + per
-    return begin, end
 
 
 def pass_tensors() -> list[tuple[str, T, int, int]]:
@@ -252,19 +244,18 @@ def run_gpu(args) -> None:
         rt.bind(f"x{w}", dev_x[w].data_ptr(), m * w)
         dev_x[w].copy_(host_x[w].view(-1))
     out_rows = sorted({rows for _, _, rows, _ in tensors})
-    y_local = {r: torch.zeros(m * (shard_rows(r, rank, world)[1] - shard_rows(r, rank, world)[0]), dtype=torch.float32, device=dev)
-               for r in out_rows}
+
+    def slice_rows(r: int, k: int) -> int:
+        b, e = shard_rows(r, k, world)
+        return e - b
+
+    # per output width: this rank's [M][rows of the slice] block, padded to the widest slice so that one
+    # all_gather_into_tensor of equal-sized chunks combines the ranks
+    widest = {r: max(slice_rows(r, k) for k in range(world)) for r in out_rows}
+    y_local = {r: torch.zeros(m * widest[r], dtype=torch.float32, device=dev) for r in out_rows}
     for r in out_rows:
-        rt.bind(f"y{r}", y_local[r].data_ptr(), y_local[r].numel())
-    gathered = {}
-    if world > 1:
-        for r in out_rows:
-            gathered[r] = [torch.empty_like(y_local[r]) if shard_rows(r, k, world)[1] - shard_rows(r, k, world)[0] ==
-                           shard_rows(r, rank, world)[1] - shard_rows(r, rank, world)[0] else
-                           torch.empty(m * (shard_rows(r, k, world)[1] - shard_rows(r, k, world)[0]), dtype=torch.float32, device=dev)
-                           for k in range(world)]
-        pair_local = torch.zeros(2 * 8, dtype=torch.float32, device=dev)
-        pair_all = [torch.empty_like(pair_local) for _ in range(world)]
+        rt.bind(f"y{r}", y_local[r].data_ptr(), m * slice_rows(r, rank))
+    gathered = {r: torch.empty(world * m * widest[r], dtype=torch.float32, device=dev) for r in out_rows} if world > 1 else {}
     ids_addr, vals_addr = rt.argmax_result()
     torch.cuda.synchronize()
 
@@ -290,10 +281,10 @@ def run_gpu(args) -> None:
         with torch.cuda.stream(stream):
             for name, t, rows, cols in tensors[:-1]:
                 rt.qmv(name, f"x{cols}", f"y{rows}", m)
-                dist.all_gather(gathered[rows], y_local[rows])
+                dist.all_gather_into_tensor(gathered[rows], y_local[rows])
             name, t, rows, cols = tensors[-1]
             rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
-            dist.all_gather(gathered[rows], y_local[rows])
+            dist.all_gather_into_tensor(gathered[rows], y_local[rows])
 
     def barrier() -> None:
         if world > 1:
@@ -323,9 +314,10 @@ def run_gpu(args) -> None:
         device_pass()
         ids, vals = rt.argmax_fetch(m, with_values=True)
         if world > 1:  # global argmax: all-gather of (value, index) pairs, highest value wins, lowest index on ties
-            pair_local[:m] = torch.tensor(vals, device=dev)
-            pair_local[8 : 8 + m] = torch.tensor([float(i) for i in ids], device=dev)
-            dist.all_gather(pair_all, pair_local)
+            pair = torch.tensor([vals, [float(i) for i in ids]], dtype=torch.float64, device=dev)
+            pairs = torch.empty((world, 2, m), dtype=torch.float64, device=dev)
+            dist.all_gather_into_tensor(pairs, pair)
+            pick_best(pairs[:, 0, :], pairs[:, 1, :].to(torch.int64)).tolist()
 
     # -- warm-up, then the timed regions
     for _ in range(max(3, args.warmup)):
