@@ -208,7 +208,9 @@ def run_gpu(args) -> None:
     with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
         books = {k: z[k].tobytes() for k in z.files}
     rt = Runtime(books["iq3s_grid"], books)
-    stream = torch.cuda.ExternalStream(rt.stream(), device=dev)
+    # the runtime launches on a stream torch owns, so that torch events, copies and NCCL order against it
+    stream = torch.cuda.Stream(device=dev)
+    rt.set_stream(stream.cuda_stream)
 
     # -- weights: seeded synthetic blocks generated on the device, this rank's row slice of every tensor
     gen = torch.Generator(device=dev)
@@ -274,17 +276,39 @@ def run_gpu(args) -> None:
         enqueue_pass()
         graph = rt.capture_end()
 
+    def sharded_pass() -> None:
+        for name, t, rows, cols in tensors[:-1]:
+            rt.qmv(name, f"x{cols}", f"y{rows}", m)
+            dist.all_gather_into_tensor(gathered[rows], y_local[rows])
+        name, t, rows, cols = tensors[-1]
+        rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
+        dist.all_gather_into_tensor(gathered[rows], y_local[rows])
+
+    # multi GPU: eager launches (kernel, all-gather, kernel, ...).  Optionally the kernels and NCCL all-gathers of a
+    # pass are captured together into one CUDA graph (VINF_BENCH_GRAPH_NCCL=1).
+    torch_graph = None
+    if world > 1 and os.environ.get("VINF_BENCH_GRAPH_NCCL") == "1":  # off by default: not validated on this pool
+        with torch.cuda.stream(stream):
+            sharded_pass()  # warm-up outside capture: kernel attributes, NCCL channels
+        torch.cuda.synchronize()
+        try:
+            torch_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(torch_graph, stream=stream):
+                sharded_pass()
+        except Exception as exc:  # noqa: BLE001
+            print(f"rank {rank}: graph capture of the sharded pass failed ({exc}); launching eagerly", file=sys.stderr)
+            torch_graph = None
+            torch.cuda.synchronize()
+
     def device_pass() -> None:
         if world == 1:
             rt.graph_launch(graph)
-            return
-        with torch.cuda.stream(stream):
-            for name, t, rows, cols in tensors[:-1]:
-                rt.qmv(name, f"x{cols}", f"y{rows}", m)
-                dist.all_gather_into_tensor(gathered[rows], y_local[rows])
-            name, t, rows, cols = tensors[-1]
-            rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
-            dist.all_gather_into_tensor(gathered[rows], y_local[rows])
+        elif torch_graph is not None:
+            with torch.cuda.stream(stream):
+                torch_graph.replay()
+        else:
+            with torch.cuda.stream(stream):
+                sharded_pass()
 
     def barrier() -> None:
         if world > 1:
@@ -328,6 +352,8 @@ def run_gpu(args) -> None:
         sampler.start()
     ms = timed(device_pass, args.steps)
     launches = rt.launch_count() - launches_before
+    if torch_graph is not None:
+        launches = args.steps * len(tensors)  # replayed by torch's graph, not counted by the runtime
     e2e_ms = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else {}
 
@@ -356,7 +382,7 @@ def run_gpu(args) -> None:
             "config": {"workload": f"synthetic-27B decode pass, M={m}: 64 x (Q6_K q/k/v/o, Q3_K gate/up, Q4_K down) + Q6_K LM head 151936x5120 "
                                    f"with fused argmax; {weight_bytes_total} weight bytes resident in HBM", "activation_rows": m,
                        "launches_per_pass": len(tensors), "l2": "pass is ~100x larger than L2 (no flush needed)",
-                       "parallelism": "single GPU, one CUDA graph per pass" if world == 1 else f"output rows sharded over {world} GPUs, NCCL all-gather per matvec"},
+                       "parallelism": "single GPU, one CUDA graph per pass" if world == 1 else f"output rows sharded over {world} GPUs, NCCL all-gather after every matvec" + (", one CUDA graph per pass" if torch_graph is not None else ", eager launches")},
             "tokens_per_s": m / (ms * 1e-3), "pct_of_8TBs": 100.0 * value / 8000.0 / world,
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * m,
                     "tokens_per_s": m / (e2e_ms * 1e-3)},
@@ -369,10 +395,12 @@ def run_gpu(args) -> None:
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
+    torch.cuda.synchronize()
+    rt.set_stream(None)
+    rt.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    rt.close()
 
 
 def main() -> None:
