@@ -153,6 +153,23 @@ int vqm_launch_count(vqm_runtime *rt, uint64_t *out);
 int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
                 unsigned *status, void *stream);
 
+/* No counterpart in the reference.  The LM-head matvec with fused argmax (like vqm_qmv_argmax) for callers that
+ * must not allocate device memory - code inside a no-allocation region of a serving loop, a process whose GPU
+ * memory was all handed out at start-up, a plugin limited to the buffers its host gave it.  Stateless: the caller
+ * passes every input and output as a device pointer (w: raw blocks, 16-byte aligned, readable 16 bytes past the
+ * end; x: [ntok][cols]; y: [ntok][rows] or NULL; out_ids: ntok ints; out_values: ntok floats or NULL; status: one
+ * word that receives a non-zero code if a bounded wait expires), and the scratch the two phases of the argmax
+ * share sits in a fixed 64.3 KB array inside the library (present on every GPU that loads the library until the
+ * process exits).  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Limits: 1 <= ntok <= 8 activation rows (more are refused with VQM_ERR_VALUE; split a wider pass into groups
+ * of 8 yourself); the launch is capped at 1024 blocks, which is what the array has partial-result slots for.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call before any stream capture.  All calls share the one array, which keeps what the
+ * last call left in it (the entry point re-zeroes the counter it needs); two calls that overlap on the GPU -
+ * different streams, or different host threads - race on it and give undefined results. */
+int vqm_qmv_argmax_static(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
+                          int *out_ids, float *out_values, unsigned *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,6 +69,7 @@ SIGNATURES: dict[str, list] = {
     "vqm_graph_destroy": [c_void_p, c_int],
     "vqm_launch_count": [c_void_p, POINTER(c_uint64)],
     "vqm_qmv_raw": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
+    "vqm_qmv_argmax_static": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 _RESTYPES = {"vqm_last_error": c_char_p, "vqm_runtime_destroy": None, "vqm_stream": c_void_p}
 

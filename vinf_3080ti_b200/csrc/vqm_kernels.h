@@ -23,6 +23,7 @@ struct MatvecArgs {
     long long row_bytes;
     int row_base;            // added to row numbers reported by the argmax (row-sharded weights)
     int overlap_launch;      // host only: launch with programmatic stream serialization (see qmv_kernel)
+    int max_grid;            // host only: upper bound on the grid (0 = none); sizes the argmax partial arrays
 };
 
 enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1 };

@@ -51,7 +51,8 @@ struct Variant {
 
     static cudaError_t launch(const MatvecArgs &a, int sm_count, cudaStream_t stream, int *grid_out) {
         if constexpr (kFits) {
-            const int grid = grid_for(a.rows, sm_count, blocks_per_sm());
+            int grid = grid_for(a.rows, sm_count, blocks_per_sm());
+            if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
             if (grid_out != nullptr) *grid_out = grid;
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3(grid);

@@ -181,6 +181,7 @@ int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int
     a.cols = t.cols;
     a.row_bytes = static_cast<long long>(t.row_bytes);
     a.overlap_launch = rt->overlap_launch;
+    a.max_grid = vqm::kMaxGrid;
     if (with_argmax) {
         a.part_val = rt->part_val;
         a.part_idx = rt->part_idx;
@@ -762,6 +763,77 @@ int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, flo
     a.cols = cols;
     a.row_bytes = static_cast<long long>(row_bytes);
     const cudaError_t err = dispatch_qmv(type, a, ntok, sm_count, static_cast<cudaStream_t>(stream), nullptr);
+    if (err != cudaSuccess) return cuda_fail("qmv launch", err);
+    return VQM_OK;
+}
+
+// ---- fused matvec + argmax for callers that cannot allocate -------------------------------------------------
+// The fused argmax needs a little device scratch between its two phases (per-block partial results and the
+// "blocks done" counter).  vqm_qmv_argmax keeps that scratch in memory the runtime allocates when it is created.
+// Some callers of this library are not able to do that: code running inside a region where the CUDA allocator
+// must not be entered (a real-time serving loop with a no-allocation rule, a process whose memory was budgeted
+// and handed out up front, a plugin that is only given the buffers its host decided on).  For them the scratch
+// lives in this fixed array inside the library image; every GPU that loads the library carries these bytes until
+// the process exits.
+constexpr int kStaticMaxBlocks = 1024;  // largest grid the scratch below can serve
+struct StaticArgmaxScratch {
+    unsigned done_counter;
+    unsigned pad[63];
+    float part_val[8 * kStaticMaxBlocks];
+    int part_idx[8 * kStaticMaxBlocks];
+};
+static __device__ __align__(256) unsigned char g_static_argmax_scratch[sizeof(StaticArgmaxScratch)];
+
+int vqm_qmv_argmax_static(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
+                          int *out_ids, float *out_values, unsigned *status, void *stream) {
+    size_t row_bytes = 0;
+    const int rc = check_shape("w", type, cols, rows, &row_bytes);
+    if (rc != VQM_OK) return rc;
+    if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8]");
+    if (cols % 32 != 0) return fail(VQM_ERR_VALUE, "matvec cols must be a multiple of 32");
+    if (w == nullptr || x == nullptr || out_ids == nullptr || status == nullptr) return fail(VQM_ERR_VALUE, "null pointer");
+    if (((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) != 0)
+        return fail(VQM_ERR_VALUE, "w, x and y must be 16-byte aligned");
+    if (vqm::grid_is_codebook(type) && codebook == nullptr) return fail(VQM_ERR_VALUE, "GGUF type %d needs its codebook", type);
+    // Set-up, once per device and with that device current: the array's name is only a host-side handle, the kernel
+    // needs the device address behind it.
+    static StaticArgmaxScratch *scratch_of_device[64] = {};
+    static int sm_count_of_device[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail("cudaGetDevice", err);
+    if (dev < 0 || dev >= 64) return fail(VQM_ERR_VALUE, "device ordinal %d is not supported", dev);
+    if (scratch_of_device[dev] == nullptr) {
+        void *ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_static_argmax_scratch);
+        if (err != cudaSuccess) return cuda_fail("cudaGetSymbolAddress", err);
+        err = cudaDeviceGetAttribute(&sm_count_of_device[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return cuda_fail("device query", err);
+        scratch_of_device[dev] = static_cast<StaticArgmaxScratch *>(ptr);
+    }
+    StaticArgmaxScratch *scratch = scratch_of_device[dev];
+    const int sm_count = sm_count_of_device[dev];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The counter must start at zero; an earlier call that was cut short could have left it otherwise.
+    err = cudaMemsetAsync(&scratch->done_counter, 0, sizeof(unsigned), st);
+    if (err != cudaSuccess) return cuda_fail("scratch reset", err);
+    vqm::MatvecArgs a{};
+    a.w = static_cast<const uint8_t *>(w);
+    a.x = x;
+    a.y = y;
+    a.codebook = static_cast<const uint8_t *>(codebook);
+    a.status = status;
+    a.part_val = scratch->part_val;
+    a.part_idx = scratch->part_idx;
+    a.done_counter = &scratch->done_counter;
+    a.out_idx = out_ids;
+    a.out_val = out_values;
+    a.rows = rows;
+    a.cols = cols;
+    a.row_bytes = static_cast<long long>(row_bytes);
+    a.max_grid = kStaticMaxBlocks;  // the launch never uses more blocks than the scratch has partial slots for
+    int grid = 0;
+    err = dispatch_qmv(type, a, ntok, sm_count, st, &grid);
     if (err != cudaSuccess) return cuda_fail("qmv launch", err);
     return VQM_OK;
 }
