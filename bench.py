@@ -38,8 +38,8 @@ from vinf_3080ti_b200.sharding import pick_best, shard_rows  # noqa: E402
 from vinf_3080ti_b200.synth import LAYER_SET, LM_HEAD, N_LAYERS, synthetic_activations, synthetic_blocks, tensor_bytes  # noqa: E402
 
 METRIC = "quant-matvec weight GB/s, synthetic-27B decode pass"
-# DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/qmv_Q3_K_17408x5120_M4.md); None until measured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture (profiles/qmv_Q3_K_17408x5120_M4.md)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 38449152
 
 
 # ---- helpers ---------------------------------------------------------------------------------------------
