@@ -125,7 +125,8 @@ int vqm_set_argmax_row_base(vqm_runtime *rt, const char *weight, int row_base);
  * reference dequantiser (engine/src/vinf/gguf/dequant.py:17-57). */
 int vqm_dequantize(vqm_runtime *rt, const char *weight, const char *out);
 
-/* set_gemm_min_rows(n) - qwen_runtime.cu:2324-2330.  Accepted for compatibility (n >= 0). */
+/* set_gemm_min_rows(n) - qwen_runtime.cu:2324-2330: passes of n or more activation rows take the tensor-core GEMM
+ * (fp16 operands, fp32 accumulation, like the reference's prompt kernel); 0 = never, every pass is fp32 matvecs. */
 int vqm_set_gemm_min_rows(vqm_runtime *rt, int n);
 /* synchronize() / mem_info() - qwen_runtime.cu:2267-2278.  synchronize also reports a kernel whose
  * bounded wait expired as VQM_ERR_CUDA. */

@@ -329,3 +329,54 @@ def test_a_captured_pass_replays_as_one_graph(rt, codebooks):
         ref = O.matvec(raw, int(t), r, c, x3 if c == 768 else x, codebooks)
         assert rel_l2(rt.read_array(f"gy{i}").reshape(2, r), ref) <= REL_L2
     rt.graph_destroy(graph)
+
+
+# ---- prompt-pass GEMM (tensor cores) --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
+def test_prompt_gemm_matches_the_matvec_path_for_every_type(rt, codebooks, t):
+    """engine/tests/test_phase31i_prefill.py:194-219: 70 x 512 weights, 37 activation rows (partial tiles), fp16
+    operands, tolerance 3e-3 * max|ref| against the fp32 matvec groups."""
+    rng = np.random.default_rng(3100 + int(t))
+    rows, cols, ntok = 70, 512, 37
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    ref = run_qmv(rt, raw, t, rows, cols, x)  # fp32 matvec, groups of 8
+    rt.set_gemm_min_rows(1)
+    try:
+        rt.zero("y")
+        rt.qmv("w", "x", "y", ntok)
+        rt.synchronize()
+        got = rt.read_array("y").reshape(ntok, rows)
+    finally:
+        rt.set_gemm_min_rows(0)
+    assert np.all(np.abs(got - ref) <= 3e-3 * np.abs(ref).max())
+    oracle = O.matvec(raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, oracle) <= 2e-3  # fp16 rounding of both operands
+
+
+@pytest.mark.parametrize("t,rows,cols,ntok", [(T.Q4_K, 1000, 5120, 512), (T.Q6_K, 321, 1024, 300), (T.IQ3_S, 64, 768, 256)],
+                         ids=lambda v: getattr(v, "name", str(v)))
+def test_prompt_gemm_larger_shapes_and_threshold(rt, clib, codebooks, t, rows, cols, ntok):
+    rng = np.random.default_rng(rows + ntok)
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    rt.upload("w", raw, int(t), cols, rows)
+    rt.alloc("x", ntok * cols)
+    rt.alloc("y", ntok * rows)
+    rt.write("x", x)
+    rt.set_gemm_min_rows(64)
+    try:
+        rt.qmv("w", "x", "y", ntok)  # >= 64 rows: GEMM
+        rt.synchronize()
+        got = rt.read_array("y").reshape(ntok, rows).copy()
+        rt.qmv("w", "x", "y", 8)  # below the threshold: still the fp32 matvec
+        rt.synchronize()
+        small = rt.read_array("y", 8 * rows).reshape(8, rows)
+    finally:
+        rt.set_gemm_min_rows(0)
+    ref = oracle_libs.c_qmv(clib, raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, ref) <= 2e-3
+    assert rel_l2(small, ref[:8]) <= REL_L2
+    with pytest.raises(ValueError):
+        rt.set_gemm_min_rows(-1)

@@ -68,6 +68,7 @@ def build(force: bool = False, jobs: int | None = None, verbose: bool = False) -
         for tid, tname in TYPES
     ]
     work.append(("vqm_aux.cu", [], OBJ / "aux.o"))
+    work.append(("vqm_gemm.cu", [], OBJ / "gemm.o"))
     work.append(("vqm_runtime.cu", [], OBJ / "runtime.o"))
     jobs = jobs or min(len(work), os.cpu_count() or 4)
     logs = []

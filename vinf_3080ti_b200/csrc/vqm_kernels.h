@@ -40,6 +40,12 @@ VQM_FOR_EACH_TYPE(VQM_DECLARE_LAUNCHER)
 
 constexpr int kMaxGrid = 4096;  // upper bound on the matvec grid (sizes the argmax partial arrays)
 
+// Prompt-pass GEMM on the tensor cores (vqm_gemm.cu).  xh: fp16 activations [ntok padded to gemm_token_tile()][cols].
+int gemm_token_tile();
+cudaError_t launch_f32_to_f16_rows(const float *x, void *xh, long long n_valid, long long n_total, cudaStream_t stream);
+cudaError_t launch_qgemm(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
+                         const uint8_t *codebook, cudaStream_t stream);
+
 cudaError_t launch_argmax_rows(const float *x, int n, int ntok, int *out, cudaStream_t stream);
 cudaError_t launch_dequant(int type, const uint8_t *w, float *out, long long numel, const uint8_t *codebook,
                            cudaStream_t stream);

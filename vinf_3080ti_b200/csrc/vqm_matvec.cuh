@@ -80,6 +80,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 
 // Bounded wait: ~2^22 polls with a short sleep after the first few hundred.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+#pragma unroll 1
     for (int i = 0; i < (1 << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 256) __nanosleep(64);
@@ -111,8 +112,11 @@ __host__ __device__ constexpr size_t matvec_smem_bytes_for() {
     return matvec_smem_bytes(TYPE, RW, M) + static_cast<size_t>(kWarps) * Step<TYPE, M, RW>::kScratch;
 }
 
+#ifndef VQM_MIN_BLOCKS
+#define VQM_MIN_BLOCKS(M) ((M) <= 4 ? 2 : 1)
+#endif
 template <int TYPE, int M, int RW>
-__global__ void __launch_bounds__(kWarps * 32, (M <= 4 ? 2 : 1)) qmv_kernel(const MatvecArgs a) {
+__global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(const MatvecArgs a) {
     using StepT = Step<TYPE, M, RW>;
     constexpr int S = stages_for(TYPE, RW);
     constexpr int XS = x_stages_for(M);

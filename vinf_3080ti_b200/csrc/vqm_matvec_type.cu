@@ -73,7 +73,7 @@ struct Variant {
 
 template <int M>
 cudaError_t launch_one(const MatvecArgs &a, int sm_count, cudaStream_t stream, int *grid_out) {
-    constexpr int kMaxRw = M <= 2 ? 8 : 4;
+    constexpr int kMaxRw = 4;  // taller chunks cost a block per SM (shared memory) and more than they save
     // smallest RW that holds a warp's share; the tallest that can run if the share needs several chunks anyway
     if (const int n = Variant<M, 1>::rows_per_warp(a.rows, sm_count); n > 0 && n <= 1) return Variant<M, 1>::launch(a, sm_count, stream, grid_out);
     if (const int n = Variant<M, 2>::rows_per_warp(a.rows, sm_count); n > 0 && n <= 2) return Variant<M, 2>::launch(a, sm_count, stream, grid_out);

@@ -80,6 +80,8 @@ struct vqm_runtime {
     // scratch of the synchronous matvec entry
     float *scratch_x = nullptr, *scratch_y = nullptr;
     size_t scratch_x_n = 0, scratch_y_n = 0;
+    void *gemm_x = nullptr;  // fp16 copy of the activations of a prompt pass
+    size_t gemm_x_len = 0;   // in elements
     int gemm_min_rows = 0;
     int overlap_launch = 1;  // programmatic dependent launch of consecutive matvecs (VINF_B200_NO_PDL=1 turns it off)
     bool capturing = false;
@@ -264,6 +266,7 @@ void vqm_runtime_destroy(vqm_runtime *rt) {
     cudaFree(rt->argmax_vals);
     cudaFree(rt->scratch_x);
     cudaFree(rt->scratch_y);
+    cudaFree(rt->gemm_x);
     if (rt->stream != nullptr) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -527,6 +530,32 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
     if (xp == nullptr) return rc;
     float *yp = find_f32(rt, y, static_cast<size_t>(t->rows) * ntok, &rc);
     if (yp == nullptr) return rc;
+    // Prompt mode (gemm_min_rows > 0, as in the reference's Runtime_qmv): passes of that many rows or more take the
+    // tensor-core GEMM, the weight is decoded once per 256 activation rows.
+    if (rt->gemm_min_rows > 0 && ntok >= rt->gemm_min_rows) {
+        const uint8_t *cb = codebook_for(rt, t->type);
+        if (vqm::grid_is_codebook(t->type) && cb == nullptr)
+            return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t->type);
+        const int tile = vqm::gemm_token_tile();
+        const size_t need = static_cast<size_t>((ntok + tile - 1) / tile * tile) * t->cols;
+        cudaError_t err = cudaSuccess;
+        if (need > rt->gemm_x_len) {
+            if ((rc = no_capture(rt, "growing the prompt-pass activation buffer")) != VQM_OK) return rc;
+            cudaStreamSynchronize(rt->stream);
+            cudaFree(rt->gemm_x);
+            rt->gemm_x = nullptr;
+            rt->gemm_x_len = 0;
+            err = cudaMalloc(&rt->gemm_x, need * 2);
+            if (err != cudaSuccess) return cuda_fail("prompt-pass activation buffer", err);
+            rt->gemm_x_len = need;
+        }
+        err = vqm::launch_f32_to_f16_rows(xp, rt->gemm_x, static_cast<long long>(ntok) * t->cols, static_cast<long long>(need), rt->stream);
+        if (err == cudaSuccess)
+            err = vqm::launch_qgemm(t->type, t->data, rt->gemm_x, yp, t->rows, t->cols, static_cast<long long>(t->row_bytes), ntok, cb, rt->stream);
+        if (err != cudaSuccess) return cuda_fail("qmv gemm launch", err);
+        count_launch(rt, 2);
+        return VQM_OK;
+    }
     // every group of 8 activation rows re-reads the weight (from L2 when it fits)
     for (int c = 0; c < ntok; c += 8) {
         const int m = ntok - c < 8 ? ntok - c : 8;
