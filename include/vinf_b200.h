@@ -154,6 +154,32 @@ int vqm_launch_count(vqm_runtime *rt, uint64_t *out);
 int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
                 unsigned *status, void *stream);
 
+/* ---- Row-sharded tensors over several GPUs (no counterpart in the reference, which is a single-GPU engine) ----
+ * Every rank (one process per GPU) holds a contiguous slice of the rows of each weight tensor.  vqm_qmv_push is
+ * qmv on the local slice fused with its all-gather: the last block of the kernel copies the slice into the gathered
+ * [ntok][rows_total] layout inside EVERY rank's exchange region with plain stores over NVLink and then raises a
+ * flag in every rank; a kernel that consumes the gathered vector waits (bounded) for the flags of all ranks.
+ *   vqm_exchange_create   allocates this rank's region and returns its 64-byte CUDA IPC handle
+ *   vqm_exchange_open     maps a peer's region from its handle
+ *   vqm_exchange_config   region addresses of all ranks (own included), this rank, and where inside a region the
+ *                         flag table (unsigned flags[n_slots][8]) and the pass counter (one unsigned) live
+ *   vqm_exchange_next_pass  advances this rank's pass counter on the stream; call once at the start of every pass
+ *   vqm_qmv_push          y = W_slice x on buffers x, y (y: [ntok][rows of the slice]); then, if slot >= 0, push y to
+ *                         dst_off inside every region as rows [row_begin, row_begin + rows) of [ntok][rows_total] and
+ *                         signal `slot`.  If wait_slot >= 0, x is only read after every rank signalled wait_slot in
+ *                         this pass (wait_lag = 0) or in the previous one (wait_lag = 1, used by the first kernel of
+ *                         a pass to make sure no rank is still reading the previous pass's vectors).
+ *                         with_argmax: also run the fused argmax (ids offset by the tensor's argmax row base).
+ * All ranks must issue the same sequence of pushes per pass.  A wait that expires sets the status word
+ * (reported by vqm_synchronize) instead of hanging. */
+int vqm_exchange_create(vqm_runtime *rt, size_t bytes, void *ipc_handle_out, uint64_t *addr);
+int vqm_exchange_open(vqm_runtime *rt, const void *ipc_handle, uint64_t *addr);
+int vqm_exchange_config(vqm_runtime *rt, int n_ranks, int rank, const uint64_t *region_addrs, size_t flag_off, size_t epoch_off,
+                        int n_slots);
+int vqm_exchange_next_pass(vqm_runtime *rt);
+int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int slot, size_t dst_off, int rows_total,
+                 int row_begin, int wait_slot, int wait_lag, int with_argmax);
+
 /* No counterpart in the reference.  The LM-head matvec with fused argmax (like vqm_qmv_argmax) for callers that
  * must not allocate device memory - code inside a no-allocation region of a serving loop, a process whose GPU
  * memory was all handed out at start-up, a plugin limited to the buffers its host gave it.  Stateless: the caller

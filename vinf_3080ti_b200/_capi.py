@@ -68,6 +68,11 @@ SIGNATURES: dict[str, list] = {
     "vqm_graph_launch": [c_void_p, c_int],
     "vqm_graph_destroy": [c_void_p, c_int],
     "vqm_launch_count": [c_void_p, POINTER(c_uint64)],
+    "vqm_exchange_create": [c_void_p, c_size_t, c_void_p, POINTER(c_uint64)],
+    "vqm_exchange_open": [c_void_p, c_void_p, POINTER(c_uint64)],
+    "vqm_exchange_config": [c_void_p, c_int, c_int, POINTER(c_uint64), c_size_t, c_size_t, c_int],
+    "vqm_exchange_next_pass": [c_void_p],
+    "vqm_qmv_push": [c_void_p, c_char_p, c_char_p, c_char_p, c_int, c_int, c_size_t, c_int, c_int, c_int, c_int, c_int],
     "vqm_qmv_raw": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "vqm_qmv_argmax_static": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }

@@ -7,6 +7,20 @@
 
 namespace vqm {
 
+// Row-sharded matvec across GPUs: where the last block of a launch copies the rank's output slice into every rank's
+// exchange region (plain remote stores over NVLink) and which flags order that against the consumers.
+struct PushInfo {
+    unsigned long long region[8];  // device address of every rank's exchange region, this rank's included
+    const unsigned *epoch;         // this rank's pass counter (device memory, advanced once per pass)
+    long long dst_off;             // byte offset, inside a region, of the gathered y[0][0] of this launch
+    long long flag_off;            // byte offset, inside a region, of the flag table: unsigned flags[slot][8 ranks]
+    int n_ranks, rank;
+    int rows_total, row_begin;     // the gathered tensor has rows_total rows; this rank's slice starts at row_begin
+    int push_slot;                 // 1 + flag slot signalled after the push (0: no push)
+    int wait_slot;                 // 1 + flag slot every rank must have signalled before x is read (0: no wait)
+    int wait_lag;                  // the wait is for epoch - wait_lag (1: the slot was signalled in the previous pass)
+};
+
 struct MatvecArgs {
     const uint8_t *w;        // raw blocks, 16-byte aligned, readable up to 15 bytes past the end
     const float *x;          // [M][cols] fp32, 16-byte aligned
@@ -24,9 +38,10 @@ struct MatvecArgs {
     int row_base;            // added to row numbers reported by the argmax (row-sharded weights)
     int overlap_launch;      // host only: launch with programmatic stream serialization (see qmv_kernel)
     int max_grid;            // host only: upper bound on the grid (0 = none); sizes the argmax partial arrays
+    PushInfo push;           // all zero when the tensor is not sharded
 };
 
-enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1 };
+enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1, kStatusPeerWaitExpired = 2 };
 
 // One launcher per GGUF type (vqm_matvec_type.cu).  m: activation rows (1..8); sm_count: SMs of the device;
 // grid_out (optional) receives the grid size used.
@@ -46,6 +61,7 @@ cudaError_t launch_f32_to_f16_rows(const float *x, void *xh, long long n_valid, 
 cudaError_t launch_qgemm(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
                          const uint8_t *codebook, cudaStream_t stream);
 
+cudaError_t launch_epoch_advance(unsigned *epoch, cudaStream_t stream);
 cudaError_t launch_argmax_rows(const float *x, int n, int ntok, int *out, cudaStream_t stream);
 cudaError_t launch_dequant(int type, const uint8_t *w, float *out, long long numel, const uint8_t *codebook,
                            cudaStream_t stream);

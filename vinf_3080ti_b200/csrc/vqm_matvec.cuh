@@ -213,6 +213,27 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
     for (; issued < S && issued < n_steps; ++issued) issue_w();
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
+        if (a.push.wait_slot > 0) {
+            // Row-sharded input: x was assembled by pushes from every rank; wait (bounded) until each of them has
+            // signalled the slot for this pass, then make their stores visible to the bulk copies below.
+            const unsigned target = *a.push.epoch - static_cast<unsigned>(a.push.wait_lag);
+            const volatile unsigned *flags = reinterpret_cast<const volatile unsigned *>(a.push.region[a.push.rank] + a.push.flag_off) +
+                                             (a.push.wait_slot - 1) * 8;
+            bool ok = true;
+            for (int p = 0; p < a.push.n_ranks && ok; ++p) {
+                int spins = 0;
+                while (static_cast<int>(flags[p] - target) < 0) {
+                    if (++spins > (1 << 22)) {
+                        ok = false;
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+            if (!ok) atomicExch(a.status, kStatusPeerWaitExpired);
+            __threadfence_system();
+            asm volatile("fence.proxy.async;" ::: "memory");
+        }
         const int n = n_steps < XS ? n_steps : XS;
         for (int s = 0; s < n; ++s) issue_x(s, s % n_seg);
     }
@@ -328,26 +349,29 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
         for (int s = 0; s < S; ++s) (void)mbar_wait_bounded(bar + s, 0);
     }
 
-    if (want_argmax) {
-        // block partial per activation row, then the last block reduces all partials
+    const bool want_push = a.push.push_slot > 0;
+    if (want_argmax || want_push) {
+        // block partials of the argmax, then the last block to finish reduces them and / or pushes the output slice
         __shared__ float s_val[kWarps][32];
         __shared__ int s_idx[kWarps][32];
         __shared__ bool s_last;
-        s_val[warp][lane] = best_v;
-        s_idx[warp][lane] = best_i;
-        __syncthreads();
-        if (threadIdx.x < M) {
-            const int t = threadIdx.x;
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-            for (int w = 0; w < kWarps; ++w)
-                for (int r = 0; r < RW; ++r)
-                    if (better(s_val[w][r * M + t], s_idx[w][r * M + t], bv, bi)) {
-                        bv = s_val[w][r * M + t];
-                        bi = s_idx[w][r * M + t];
-                    }
-            a.part_val[t * gridDim.x + blockIdx.x] = bv;
-            a.part_idx[t * gridDim.x + blockIdx.x] = bi;
+        if (want_argmax) {
+            s_val[warp][lane] = best_v;
+            s_idx[warp][lane] = best_i;
+            __syncthreads();
+            if (threadIdx.x < M) {
+                const int t = threadIdx.x;
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                for (int w = 0; w < kWarps; ++w)
+                    for (int r = 0; r < RW; ++r)
+                        if (better(s_val[w][r * M + t], s_idx[w][r * M + t], bv, bi)) {
+                            bv = s_val[w][r * M + t];
+                            bi = s_idx[w][r * M + t];
+                        }
+                a.part_val[t * gridDim.x + blockIdx.x] = bv;
+                a.part_idx[t * gridDim.x + blockIdx.x] = bi;
+            }
         }
         __threadfence();
         __syncthreads();
@@ -355,7 +379,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
         __syncthreads();
         if (s_last) {
             __threadfence();
-            if (warp < M) {
+            if (want_argmax && warp < M) {
                 const int t = warp;
                 float bv = -INFINITY;
                 int bi = 0x7fffffff;
@@ -379,6 +403,35 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                 if (lane == 0) {
                     a.out_idx[t] = bi == 0x7fffffff ? bi : bi + a.row_base;
                     if (a.out_val != nullptr) a.out_val[t] = bv;
+                }
+            }
+            if (want_push) {
+                // All rows of this rank's slice are in a.y ([M][a.rows]); copy them into the gathered [M][rows_total]
+                // layout of every rank's region with plain (remote) stores, then signal the slot to every rank.
+                const unsigned epoch = *a.push.epoch;
+                const bool vec = ((a.rows | a.push.row_begin | a.push.rows_total) & 3) == 0;
+                for (int p = 0; p < a.push.n_ranks; ++p) {
+                    float *dst = reinterpret_cast<float *>(a.push.region[p] + a.push.dst_off);
+                    if (vec) {
+                        const int n4 = a.rows >> 2;
+                        for (int e = threadIdx.x; e < M * n4; e += blockDim.x) {
+                            const int t = e / n4, i = e - t * n4;
+                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(a.y + static_cast<size_t>(t) * a.rows) + i);
+                            reinterpret_cast<float4 *>(dst + static_cast<size_t>(t) * a.push.rows_total + a.push.row_begin)[i] = v;
+                        }
+                    } else {
+                        for (int e = threadIdx.x; e < M * a.rows; e += blockDim.x) {
+                            const int t = e / a.rows, i = e - t * a.rows;
+                            dst[static_cast<size_t>(t) * a.push.rows_total + a.push.row_begin + i] = __ldcg(a.y + e);
+                        }
+                    }
+                }
+                __threadfence_system();
+                __syncthreads();
+                if (threadIdx.x < a.push.n_ranks) {
+                    volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(a.push.region[threadIdx.x] + a.push.flag_off) +
+                                              (a.push.push_slot - 1) * 8 + a.push.rank;
+                    *flag = epoch;
                 }
             }
             if (threadIdx.x == 0) *a.done_counter = 0;

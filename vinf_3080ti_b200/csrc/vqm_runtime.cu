@@ -82,6 +82,11 @@ struct vqm_runtime {
     size_t scratch_x_n = 0, scratch_y_n = 0;
     void *gemm_x = nullptr;  // fp16 copy of the activations of a prompt pass
     size_t gemm_x_len = 0;   // in elements
+    // exchange of row-sharded outputs between ranks
+    void *exchange_own = nullptr;           // region this runtime allocated
+    std::vector<void *> exchange_opened;    // peers' regions mapped through IPC handles
+    vqm::PushInfo push{};                   // regions, rank, flag table, epoch
+    int exchange_slots = 0;
     int gemm_min_rows = 0;
     int overlap_launch = 1;  // programmatic dependent launch of consecutive matvecs (VINF_B200_NO_PDL=1 turns it off)
     bool capturing = false;
@@ -169,7 +174,8 @@ int check_shape(const char *name, int type, int cols, int rows, size_t *row_byte
 }
 
 // Launches y = W x for m <= 8 rows of x, optionally with the fused argmax.
-int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int m, bool with_argmax) {
+int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int m, bool with_argmax,
+                 const vqm::PushInfo *push = nullptr) {
     const uint8_t *cb = codebook_for(rt, t.type);
     if (vqm::grid_is_codebook(t.type) && cb == nullptr)
         return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t.type);
@@ -184,6 +190,10 @@ int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int
     a.row_bytes = static_cast<long long>(t.row_bytes);
     a.overlap_launch = rt->overlap_launch;
     a.max_grid = vqm::kMaxGrid;
+    if (push != nullptr) {
+        a.push = *push;
+        a.done_counter = rt->done_counter;
+    }
     if (with_argmax) {
         a.part_val = rt->part_val;
         a.part_idx = rt->part_idx;
@@ -267,6 +277,8 @@ void vqm_runtime_destroy(vqm_runtime *rt) {
     cudaFree(rt->scratch_x);
     cudaFree(rt->scratch_y);
     cudaFree(rt->gemm_x);
+    for (void *p : rt->exchange_opened) cudaIpcCloseMemHandle(p);
+    cudaFree(rt->exchange_own);
     if (rt->stream != nullptr) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -543,6 +555,8 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
             if ((rc = no_capture(rt, "growing the prompt-pass activation buffer")) != VQM_OK) return rc;
             cudaStreamSynchronize(rt->stream);
             cudaFree(rt->gemm_x);
+    for (void *p : rt->exchange_opened) cudaIpcCloseMemHandle(p);
+    cudaFree(rt->exchange_own);
             rt->gemm_x = nullptr;
             rt->gemm_x_len = 0;
             err = cudaMalloc(&rt->gemm_x, need * 2);
@@ -762,6 +776,94 @@ int vqm_graph_destroy(vqm_runtime *rt, int graph_id) {
 int vqm_launch_count(vqm_runtime *rt, uint64_t *out) {
     *out = rt->launches;
     return VQM_OK;
+}
+
+// ---- row-sharded tensors: exchange regions and the fused push -----------------------------------------------
+
+int vqm_exchange_create(vqm_runtime *rt, size_t bytes, void *ipc_handle_out, uint64_t *addr) {
+    if (bytes == 0 || ipc_handle_out == nullptr || addr == nullptr) return fail(VQM_ERR_VALUE, "bad exchange region arguments");
+    if (rt->exchange_own != nullptr) return fail(VQM_ERR_VALUE, "this runtime already has an exchange region");
+    const int rc = no_capture(rt, "exchange_create");
+    if (rc != VQM_OK) return rc;
+    cudaError_t err = cudaMalloc(&rt->exchange_own, bytes);
+    if (err == cudaSuccess) err = cudaMemset(rt->exchange_own, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (err == cudaSuccess) err = cudaIpcGetMemHandle(&h, rt->exchange_own);
+    if (err != cudaSuccess) {
+        cudaFree(rt->exchange_own);
+        rt->exchange_own = nullptr;
+        return cuda_fail("exchange region", err);
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(ipc_handle_out, &h, sizeof(h));
+    *addr = reinterpret_cast<uintptr_t>(rt->exchange_own);
+    return VQM_OK;
+}
+
+int vqm_exchange_open(vqm_runtime *rt, const void *ipc_handle, uint64_t *addr) {
+    if (ipc_handle == nullptr || addr == nullptr) return fail(VQM_ERR_VALUE, "bad exchange region arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handle, sizeof(h));
+    void *p = nullptr;
+    const cudaError_t err = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (err != cudaSuccess) return cuda_fail("cudaIpcOpenMemHandle", err);
+    rt->exchange_opened.push_back(p);
+    *addr = reinterpret_cast<uintptr_t>(p);
+    return VQM_OK;
+}
+
+int vqm_exchange_config(vqm_runtime *rt, int n_ranks, int rank, const uint64_t *region_addrs, size_t flag_off, size_t epoch_off,
+                        int n_slots) {
+    if (n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks || region_addrs == nullptr || n_slots < 1)
+        return fail(VQM_ERR_VALUE, "exchange_config: 1..8 ranks, 0 <= rank < ranks, at least one slot");
+    if ((flag_off & 3u) != 0 || (epoch_off & 3u) != 0) return fail(VQM_ERR_VALUE, "flag and epoch offsets must be 4-byte aligned");
+    vqm::PushInfo p{};
+    for (int i = 0; i < n_ranks; ++i) {
+        if (region_addrs[i] == 0 || (region_addrs[i] & 15u) != 0) return fail(VQM_ERR_VALUE, "region %d is not a 16-byte aligned address", i);
+        p.region[i] = region_addrs[i];
+    }
+    p.n_ranks = n_ranks;
+    p.rank = rank;
+    p.flag_off = static_cast<long long>(flag_off);
+    p.epoch = reinterpret_cast<const unsigned *>(region_addrs[rank] + epoch_off);
+    rt->push = p;
+    rt->exchange_slots = n_slots;
+    return VQM_OK;
+}
+
+int vqm_exchange_next_pass(vqm_runtime *rt) {
+    if (rt->push.n_ranks == 0) return fail(VQM_ERR_VALUE, "exchange_config has not been called");
+    const cudaError_t err = vqm::launch_epoch_advance(const_cast<unsigned *>(rt->push.epoch), rt->stream);
+    if (err != cudaSuccess) return cuda_fail("epoch advance", err);
+    count_launch(rt);
+    return VQM_OK;
+}
+
+int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int slot, size_t dst_off, int rows_total,
+                 int row_begin, int wait_slot, int wait_lag, int with_argmax) {
+    if (rt->push.n_ranks == 0) return fail(VQM_ERR_VALUE, "exchange_config has not been called");
+    if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8]");
+    if (slot < -1 || slot >= rt->exchange_slots || wait_slot < -1 || wait_slot >= rt->exchange_slots || wait_lag < 0 || wait_lag > 1)
+        return fail(VQM_ERR_VALUE, "slot out of range");
+    int rc = VQM_OK;
+    Tensor *t = find_tensor(rt, weight, &rc);
+    if (t == nullptr) return rc;
+    if (t->cols % 32 != 0) return fail(VQM_ERR_VALUE, "%s: matvec cols must be a multiple of 32", weight);
+    if (rows_total < t->rows || row_begin < 0 || row_begin + t->rows > rows_total || (dst_off & 15u) != 0)
+        return fail(VQM_ERR_VALUE, "%s: slice [%d, %d) does not fit %d rows, or dst_off is not 16-byte aligned", weight, row_begin,
+                    row_begin + t->rows, rows_total);
+    const float *xp = find_f32(rt, x, static_cast<size_t>(t->cols) * ntok, &rc);
+    if (xp == nullptr) return rc;
+    float *yp = find_f32(rt, y, static_cast<size_t>(t->rows) * ntok, &rc);
+    if (yp == nullptr) return rc;
+    vqm::PushInfo p = rt->push;
+    p.dst_off = static_cast<long long>(dst_off);
+    p.rows_total = rows_total;
+    p.row_begin = row_begin;
+    p.push_slot = slot + 1;
+    p.wait_slot = wait_slot + 1;
+    p.wait_lag = wait_lag;
+    return launch_group(rt, *t, xp, yp, ntok, with_argmax != 0, &p);
 }
 
 int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,

@@ -274,6 +274,34 @@ class Runtime:
         _capi.check(self._lib.vqm_launch_count(self._h, ctypes.byref(out)))
         return out.value
 
+    # ---- row-sharded tensors over several GPUs (no reference counterpart) -----------------------------------------
+    def exchange_create(self, nbytes: int) -> tuple[bytes, int]:
+        """Allocates this rank's exchange region; returns (64-byte CUDA IPC handle, device address)."""
+        handle = ctypes.create_string_buffer(64)
+        addr = ctypes.c_uint64()
+        _capi.check(self._lib.vqm_exchange_create(self._h, int(nbytes), handle, ctypes.byref(addr)))
+        return handle.raw, addr.value
+
+    def exchange_open(self, handle: bytes) -> int:
+        """Maps a peer's exchange region from its IPC handle; returns its address in this process."""
+        addr = ctypes.c_uint64()
+        buf = ctypes.create_string_buffer(handle, 64)
+        _capi.check(self._lib.vqm_exchange_open(self._h, buf, ctypes.byref(addr)))
+        return addr.value
+
+    def exchange_config(self, rank: int, region_addrs: Sequence[int], flag_off: int, epoch_off: int, n_slots: int) -> None:
+        arr = (ctypes.c_uint64 * len(region_addrs))(*region_addrs)
+        _capi.check(self._lib.vqm_exchange_config(self._h, len(region_addrs), int(rank), arr, int(flag_off), int(epoch_off), int(n_slots)))
+
+    def exchange_next_pass(self) -> None:
+        _capi.check(self._lib.vqm_exchange_next_pass(self._h))
+
+    def qmv_push(self, weight: str, x: str, y: str, ntok: int, slot: int, dst_off: int, rows_total: int, row_begin: int,
+                 wait_slot: int = -1, wait_lag: int = 0, with_argmax: bool = False) -> None:
+        """qmv on this rank's row slice fused with its all-gather (see include/vinf_b200.h)."""
+        _capi.check(self._lib.vqm_qmv_push(self._h, _name(weight), _name(x), _name(y), int(ntok), int(slot), int(dst_off), int(rows_total),
+                                           int(row_begin), int(wait_slot), int(wait_lag), int(with_argmax)))
+
     # ---- residency machinery of the reference: everything is resident here ------------------------------
     # (engine/csrc/megakernel/qwen_runtime.cu:1485-1811; engine/src/vinf/gguf/residency.py:256-354)
     def vram_bytes(self) -> int:

@@ -57,3 +57,28 @@ def pick_best(values: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     best = values.max(dim=0).values
     candidate = torch.where((values == best) & (values > float("-inf")), ids, torch.full_like(ids, NO_INDEX))
     return candidate.min(dim=0).values
+
+
+class ExchangeLayout:
+    """Byte layout of a rank's exchange region for the fused push (Runtime.qmv_push): gathered vectors first, then
+    the flag table unsigned[n_slots][8], then the pass counter."""
+
+    def __init__(self, data_bytes: int, n_slots: int) -> None:
+        self.data_bytes = (int(data_bytes) + 255) // 256 * 256
+        self.n_slots = int(n_slots)
+        self.flag_off = self.data_bytes
+        self.epoch_off = self.flag_off + self.n_slots * 8 * 4
+        self.total = (self.epoch_off + 4 + 255) // 256 * 256
+
+
+def connect_exchange(rt, layout: ExchangeLayout, group=None) -> list[int]:
+    """Creates this rank's exchange region, trades CUDA IPC handles with the other ranks of the process group and
+    configures the runtime.  Returns every rank's region address as seen from this process."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    handle, own = rt.exchange_create(layout.total)
+    handles: list = [None] * world
+    dist.all_gather_object(handles, handle, group=group)
+    addrs = [own if k == rank else rt.exchange_open(handles[k]) for k in range(world)]
+    rt.exchange_config(rank, addrs, layout.flag_off, layout.epoch_off, layout.n_slots)
+    dist.barrier(group)
+    return addrs
