@@ -276,7 +276,7 @@ def run_gpu(args) -> None:
         enqueue_pass()
         graph = rt.capture_end()
 
-    def sharded_pass() -> None:
+    def sharded_pass() -> None:  # NCCL arm: kernel, all-gather, kernel, ... launched eagerly
         for name, t, rows, cols in tensors[:-1]:
             rt.qmv(name, f"x{cols}", f"y{rows}", m)
             dist.all_gather_into_tensor(gathered[rows], y_local[rows])
@@ -284,24 +284,53 @@ def run_gpu(args) -> None:
         rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
         dist.all_gather_into_tensor(gathered[rows], y_local[rows])
 
-    # multi GPU: eager launches (kernel, all-gather, kernel, ...).  Optionally the kernels and NCCL all-gathers of a
-    # pass are captured together into one CUDA graph (VINF_BENCH_GRAPH_NCCL=1).
+    # Fused arm (default): every matvec pushes its slice into the gathered vector of every rank from its own epilogue and
+    # the next matvec waits for all ranks' flags - the dependency chain of a tensor-parallel decoder.  One gathered
+    # vector per kind of tensor (q, k, v, o, gate, up, down, logits); one flag slot per launch of the pass; the whole
+    # pass is one CUDA graph per rank and contains no collective.
+    use_push = world > 1 and args.gather == "push"
+    push_mode = os.environ.get("VINF_BENCH_PUSH_MODE", "full")  # experiments: "nowait" (push, no flag waits), "none" (sharded kernels only)
+    if use_push:
+        from vinf_3080ti_b200.sharding import ExchangeLayout, connect_exchange
+
+        kinds = {}
+        off = 0
+        for name, t, rows, cols in tensors:
+            kind = name.split(".")[-1]
+            if kind not in kinds:
+                kinds[kind] = off
+                off += (4 * m * rows + 255) // 256 * 256
+        layout = ExchangeLayout(off, n_slots=len(tensors))
+        connect_exchange(rt, layout)
+
+        # the launch whose flags a launch waits for: the last one that produced (part of) its input
+        producer_kind = {"attn_q": "ffn_down", "attn_k": "ffn_down", "attn_v": "ffn_down", "attn_o": "attn_v", "ffn_gate": "attn_o",
+                         "ffn_up": "attn_o", "ffn_down": "ffn_up", "output": "ffn_down"}
+        last_of_kind: dict[str, int] = {}
+        wait_for = []
+        for i, (name, t, rows, cols) in enumerate(tensors):
+            wait_for.append(last_of_kind.get(producer_kind[name.split(".")[-1]], len(tensors) - 1))  # first layer: previous pass's last launch
+            last_of_kind[name.split(".")[-1]] = i
+
+        def push_pass() -> None:
+            rt.exchange_next_pass()
+            for i, (name, t, rows, cols) in enumerate(tensors):
+                b, e = local_rows[name]
+                rt.qmv_push(name, f"x{cols}", f"y{rows}", m, slot=i if push_mode != "none" else -1, dst_off=kinds[name.split(".")[-1]],
+                            rows_total=rows, row_begin=b, wait_slot=wait_for[i] if push_mode == "full" else -1,
+                            wait_lag=1 if wait_for[i] >= i else 0, with_argmax=(i == len(tensors) - 1))
+
+        push_pass()
+        rt.synchronize()
+        dist.barrier()
+        rt.capture_begin()
+        push_pass()
+        graph = rt.capture_end()
+
     torch_graph = None
-    if world > 1 and os.environ.get("VINF_BENCH_GRAPH_NCCL") == "1":  # off by default: not validated on this pool
-        with torch.cuda.stream(stream):
-            sharded_pass()  # warm-up outside capture: kernel attributes, NCCL channels
-        torch.cuda.synchronize()
-        try:
-            torch_graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(torch_graph, stream=stream):
-                sharded_pass()
-        except Exception as exc:  # noqa: BLE001
-            print(f"rank {rank}: graph capture of the sharded pass failed ({exc}); launching eagerly", file=sys.stderr)
-            torch_graph = None
-            torch.cuda.synchronize()
 
     def device_pass() -> None:
-        if world == 1:
+        if world == 1 or use_push:
             rt.graph_launch(graph)
         elif torch_graph is not None:
             with torch.cuda.stream(stream):
@@ -382,7 +411,9 @@ def run_gpu(args) -> None:
             "config": {"workload": f"synthetic-27B decode pass, M={m}: 64 x (Q6_K q/k/v/o, Q3_K gate/up, Q4_K down) + Q6_K LM head 151936x5120 "
                                    f"with fused argmax; {weight_bytes_total} weight bytes resident in HBM", "activation_rows": m,
                        "launches_per_pass": len(tensors), "l2": "pass is ~100x larger than L2 (no flush needed)",
-                       "parallelism": "single GPU, one CUDA graph per pass" if world == 1 else f"output rows sharded over {world} GPUs, NCCL all-gather after every matvec" + (", one CUDA graph per pass" if torch_graph is not None else ", eager launches")},
+                       "parallelism": "single GPU, one CUDA graph per pass" if world == 1 else (f"output rows sharded over {world} GPUs; every matvec pushes its slice into all ranks' gathered vector over NVLink from its epilogue "
+                                        "and waits for the flags of the launch that produced its input (decoder dependency chain); one CUDA graph per rank, no collective" if use_push else
+                                        f"output rows sharded over {world} GPUs, NCCL all-gather after every matvec, eager launches")},
             "tokens_per_s": m / (ms * 1e-3), "pct_of_8TBs": 100.0 * value / 8000.0 / world,
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * m,
                     "tokens_per_s": m / (e2e_ms * 1e-3)},
@@ -410,6 +441,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--m", type=int, default=4, help="activation rows per pass (1..8)")
+    ap.add_argument("--gather", default="push", choices=["push", "nccl"],
+                    help="multi-GPU: how output slices are combined - fused peer-memory push from the kernel (default) or NCCL all-gather")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline leg (0 = skip)")
     args = ap.parse_args()
     if args.impl == "reference":

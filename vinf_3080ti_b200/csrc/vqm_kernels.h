@@ -7,8 +7,8 @@
 
 namespace vqm {
 
-// Row-sharded matvec across GPUs: where the last block of a launch copies the rank's output slice into every rank's
-// exchange region (plain remote stores over NVLink) and which flags order that against the consumers.
+// Row-sharded matvec across GPUs: where a launch stores its outputs inside every rank's exchange region (plain remote
+// stores over NVLink, issued by the lane that holds the output) and which flags order that against the consumers.
 struct PushInfo {
     unsigned long long region[8];  // device address of every rank's exchange region, this rank's included
     const unsigned *epoch;         // this rank's pass counter (device memory, advanced once per pass)

@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
             const unsigned target = *a.push.epoch - static_cast<unsigned>(a.push.wait_lag);
             const volatile unsigned *flags = reinterpret_cast<const volatile unsigned *>(a.push.region[a.push.rank] + a.push.flag_off) +
                                              (a.push.wait_slot - 1) * 8;
-            bool ok = true;
+            bool ok = *reinterpret_cast<volatile unsigned *>(a.status) == 0;  // after one expiry later kernels do not wait again
             for (int p = 0; p < a.push.n_ranks && ok; ++p) {
                 int spins = 0;
                 while (static_cast<int>(flags[p] - target) < 0) {
@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                     __nanosleep(100);
                 }
             }
-            if (!ok) atomicExch(a.status, kStatusPeerWaitExpired);
+            if (!ok) atomicCAS(a.status, 0u, kStatusPeerWaitExpired);
             __threadfence_system();
             asm volatile("fence.proxy.async;" ::: "memory");
         }
@@ -319,6 +319,12 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                     const int r = lane / M, t = lane % M, row = row0 + r;
                     if (r < nrows) {
                         if (a.y != nullptr) a.y[static_cast<size_t>(t) * a.rows + row] = mine;
+                        if (a.push.push_slot > 0) {
+                            // row-sharded: the value also goes straight into every rank's gathered [M][rows_total] vector
+                            const size_t at = static_cast<size_t>(t) * a.push.rows_total + a.push.row_begin + row;
+                            for (int p = 0; p < a.push.n_ranks; ++p)
+                                reinterpret_cast<float *>(a.push.region[p] + a.push.dst_off)[at] = mine;
+                        }
                         if (want_argmax && better(mine, row, best_v, best_i)) {
                             best_v = mine;
                             best_i = row;
@@ -373,12 +379,15 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                 a.part_idx[t * gridDim.x + blockIdx.x] = bi;
             }
         }
+        // Release at GPU scope: this block's stores (remote ones included) happen before its count below; the last
+        // block's system-scope fence is cumulative over everything it has observed through the counter.
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) s_last = atomicAdd(a.done_counter, 1u) == gridDim.x - 1;
         __syncthreads();
         if (s_last) {
-            __threadfence();
+            if (want_push) __threadfence_system();
+            else __threadfence();
             if (want_argmax && warp < M) {
                 const int t = warp;
                 float bv = -INFINITY;
@@ -405,34 +414,12 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                     if (a.out_val != nullptr) a.out_val[t] = bv;
                 }
             }
-            if (want_push) {
-                // All rows of this rank's slice are in a.y ([M][a.rows]); copy them into the gathered [M][rows_total]
-                // layout of every rank's region with plain (remote) stores, then signal the slot to every rank.
-                const unsigned epoch = *a.push.epoch;
-                const bool vec = ((a.rows | a.push.row_begin | a.push.rows_total) & 3) == 0;
-                for (int p = 0; p < a.push.n_ranks; ++p) {
-                    float *dst = reinterpret_cast<float *>(a.push.region[p] + a.push.dst_off);
-                    if (vec) {
-                        const int n4 = a.rows >> 2;
-                        for (int e = threadIdx.x; e < M * n4; e += blockDim.x) {
-                            const int t = e / n4, i = e - t * n4;
-                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(a.y + static_cast<size_t>(t) * a.rows) + i);
-                            reinterpret_cast<float4 *>(dst + static_cast<size_t>(t) * a.push.rows_total + a.push.row_begin)[i] = v;
-                        }
-                    } else {
-                        for (int e = threadIdx.x; e < M * a.rows; e += blockDim.x) {
-                            const int t = e / a.rows, i = e - t * a.rows;
-                            dst[static_cast<size_t>(t) * a.push.rows_total + a.push.row_begin + i] = __ldcg(a.y + e);
-                        }
-                    }
-                }
-                __threadfence_system();
-                __syncthreads();
-                if (threadIdx.x < a.push.n_ranks) {
-                    volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(a.push.region[threadIdx.x] + a.push.flag_off) +
-                                              (a.push.push_slot - 1) * 8 + a.push.rank;
-                    *flag = epoch;
-                }
+            if (want_push && threadIdx.x < a.push.n_ranks) {
+                // every block made its remote stores visible (system-wide fence below) before it counted itself done:
+                // raise this rank's flag for the slot in every rank's table
+                volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(a.push.region[threadIdx.x] + a.push.flag_off) +
+                                          (a.push.push_slot - 1) * 8 + a.push.rank;
+                *flag = *a.push.epoch;
             }
             if (threadIdx.x == 0) *a.done_counter = 0;
         }

@@ -215,7 +215,8 @@ int check_status_word(vqm_runtime *rt, const char *ctx) {
     if (err != cudaSuccess) return cuda_fail(ctx, err);
     if (host != 0) {
         cudaMemsetAsync(rt->status, 0, sizeof(unsigned), rt->stream);
-        return fail(VQM_ERR_CUDA, "%s failed: a kernel gave up waiting for its weight copies (status %u)", ctx, host);
+        return fail(VQM_ERR_CUDA, "%s failed: a kernel gave up a bounded wait (status %u: 1 = its own weight copies, 2 = another rank's push)",
+                    ctx, host);
     }
     return VQM_OK;
 }
