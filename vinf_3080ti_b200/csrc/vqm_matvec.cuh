@@ -212,28 +212,37 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
     int issued = 0;
     for (; issued < S && issued < n_steps; ++issued) issue_w();
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (threadIdx.x == 0) {
-        if (a.push.wait_slot > 0) {
-            // Row-sharded input: x was assembled by pushes from every rank; wait (bounded) until each of them has
-            // signalled the slot for this pass, then make their stores visible to the bulk copies below.
-            const unsigned target = *a.push.epoch - static_cast<unsigned>(a.push.wait_lag);
-            const volatile unsigned *flags = reinterpret_cast<const volatile unsigned *>(a.push.region[a.push.rank] + a.push.flag_off) +
-                                             (a.push.wait_slot - 1) * 8;
-            bool ok = *reinterpret_cast<volatile unsigned *>(a.status) == 0;  // after one expiry later kernels do not wait again
-            for (int p = 0; p < a.push.n_ranks && ok; ++p) {
-                int spins = 0;
-                while (static_cast<int>(flags[p] - target) < 0) {
-                    if (++spins > (1 << 22)) {
-                        ok = false;
-                        break;
-                    }
-                    __nanosleep(100);
+    if (warp == 0 && a.push.wait_slot > 0) {
+        // Row-sharded input: x was assembled by pushes from every rank.  Lane p waits (bounded) until rank p has
+        // signalled the slot for this pass - the flags are polled in parallel, one L2 round trip when they are already
+        // up - then the ranks' stores are made visible to the bulk copies below.
+        bool ok = *reinterpret_cast<volatile unsigned *>(a.status) == 0;  // after one expiry later kernels do not wait again
+        if (lane < a.push.n_ranks && ok) {
+            const volatile unsigned *flag = reinterpret_cast<const volatile unsigned *>(a.push.region[a.push.rank] + a.push.flag_off) +
+                                            (a.push.wait_slot - 1) * 8 + lane;
+            const unsigned target = *reinterpret_cast<const volatile unsigned *>(a.push.epoch) - static_cast<unsigned>(a.push.wait_lag);
+            int spins = 0;
+            auto acquire = [](const volatile unsigned *p) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+                return v;
+            };
+            while (static_cast<int>(acquire(flag) - target) < 0) {
+                if (++spins > (1 << 22)) {
+                    ok = false;
+                    break;
                 }
+                __nanosleep(40);
             }
-            if (!ok) atomicCAS(a.status, 0u, kStatusPeerWaitExpired);
-            __threadfence_system();
-            asm volatile("fence.proxy.async;" ::: "memory");
         }
+        ok = __all_sync(0xffffffffu, ok);
+        if (lane == 0) {
+            if (!ok) atomicCAS(a.status, 0u, kStatusPeerWaitExpired);
+            asm volatile("fence.proxy.async;" ::: "memory");  // the acquired stores, before the bulk copies read them
+        }
+        __syncwarp();
+    }
+    if (threadIdx.x == 0) {
         const int n = n_steps < XS ? n_steps : XS;
         for (int s = 0; s < n; ++s) issue_x(s, s % n_seg);
     }
