@@ -30,6 +30,7 @@
 #include "vqm_kernels.h"
 #include "vqm_steps.cuh"
 #include "vqm_steps_kquants.cuh"
+#include "vqm_steps_iq4.cuh"
 
 namespace vqm {
 
