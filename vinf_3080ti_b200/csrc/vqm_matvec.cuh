@@ -325,6 +325,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                         if (lane == r * M + t) mine = s;
                         acc[r][t] = 0ull;
                     }
+                mine *= StepT::kOutScale;  // exact: 1 or a power of two (see bytes_to_subpair)
                 if (lane < RW * M) {
                     const int r = lane / M, t = lane % M, row = row0 + r;
                     if (r < nrows) {

@@ -99,6 +99,23 @@ __device__ __forceinline__ f32x2 bytes_to_pair(uint32_t w, f32x2 neg_magic) {
     return add2(p, neg_magic);
 }
 
+// Byte K of `w` as the subnormal float byte * 2^-141 (the byte sits in bits 8..15 of an otherwise zero word): the
+// cheapest exact integer -> float there is, one byte permute and no rebasing add.  fp32 multiplies and FMAs take
+// subnormal inputs at full rate.  The tuned decoders multiply it by a group scale carrying an extra 2^64, which yields
+// the dequantised weight times 2^-77 (exact, a power-of-two factor); sums are kept in that scale and the kernel
+// multiplies each finished output by kOutScale = 2^77.  With fp16 block scales the scaled terms stay inside the normal
+// fp32 range (largest group scale 65504 * 128 * 2^64 < 2^88; a weight of 2^-24 times 2^-77 is 2^-101).
+constexpr float kSubScale = 0x1p64f;     // folded into the group scales
+constexpr float kSubWeight = 0x1p-77f;   // dequantised weight -> value held in the sums (2^-141 * 2^64)
+constexpr float kSubOutScale = 0x1p77f;  // applied once per output
+template <int K0, int K1>
+__device__ __forceinline__ f32x2 bytes_to_subpair(uint32_t w) {
+    const uint32_t lo = __byte_perm(w, 0u, 0x4404 | (K0 << 4)), hi = __byte_perm(w, 0u, 0x4404 | (K1 << 4));
+    f32x2 p;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "r"(lo), "r"(hi));
+    return p;
+}
+
 // Four consecutive staged activations (16-byte aligned) as two packed pairs.
 struct X4 {
     f32x2 p01, p23;
@@ -142,6 +159,7 @@ __device__ __forceinline__ void dispatch_rows(int nrows, Args &&...args) {
 template <int TYPE, int M, int RW>
 struct Step {
     static constexpr int kScratch = 0;
+    static constexpr float kOutScale = 1.0f;  // factor between the sums and the outputs
     static __device__ __forceinline__ void run(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t, uint32_t table, uint32_t xs,
                                                int cols, int nrows, f32x2 (&acc)[RW][M], int lane) {
         constexpr int SLOT = slot_bytes(TYPE), CPB = chunk_block(TYPE) / 8, BB = chunk_block_bytes(TYPE);

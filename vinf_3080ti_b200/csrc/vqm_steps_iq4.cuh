@@ -17,6 +17,7 @@ namespace vqm {
 template <int M, int RW>
 struct Step<kIQ4_XS, M, RW> {
     static constexpr int kScratch = RW * 4 * 8 * 8;  // (dl, dl) per (row, block, group)
+    static constexpr float kOutScale = 1.0f;
 
     template <int NR>
     struct Pass {

@@ -1,11 +1,13 @@
 // Tuned step decoders for Q4_K, Q6_K and Q3_K (the types of the 27B layer set).  See vqm_steps.cuh for the interface.
 //
-// Common idea: the per-weight work is "raw field -> float" (one byte permute per weight, one packed add per two), one
-// packed multiply by the group scale dl (exact: the product has at most 23 significant bits, it is the dequantised
-// weight without its minimum) and one FMA per activation row.  The minimum of the types that carry one is taken out
-// of the sum:  sum_i (dl q_i - ml) x_i = sum_i (dl q_i) x_i - ml * sum_i x_i.  Sub-scales are decoded once per step
-// by a scale pass (word-wide mask arithmetic, four sub-scales per lane) into a per-warp table of (dl, dl) pairs.
-// The sequence of operations per output does not depend on the number of activation rows.
+// Common idea: the per-weight work is "raw field -> float" (one byte permute: the field becomes the subnormal
+// field * 2^-141, see bytes_to_subpair), one packed multiply or FMA per two weights with the group scale dl * 2^64
+// (exact: the product is the dequantised weight, without its minimum, times 2^-77) and one FMA per activation row.
+// The minimum of the types that carry one is taken out of the sum:
+//   sum_i (dl q_i - ml) x_i = sum_i (dl q_i) x_i - ml * sum_i x_i.
+// Sub-scales are decoded once per step by a scale pass (word-wide mask arithmetic, four sub-scales per lane) into a
+// per-warp table of (dl, dl) pairs.  The sequence of operations per output does not depend on the number of
+// activation rows.
 #pragma once
 
 #include "vqm_steps.cuh"
@@ -27,9 +29,37 @@ struct Step<kQ4_K, M, RW> {
     // piece 2w: scales, piece 2w + 1: mins of pair p = 2hh + w; slot (row * 4 + block) * 2 + hh of 16 bytes in each piece
     static constexpr int kPiece = RW * 4 * 2 * 16 + 32;  // + 32: consecutive pieces start 8 banks apart
     static constexpr int kScratch = 4 * kPiece;
+    static constexpr float kOutScale = kSubOutScale;
 
     template <int NR>
     struct Pass {
+        // One block of every row: lane i -> nibble word i.
+        static __device__ __forceinline__ void block_dot(uint32_t wl, uint32_t el, uint32_t xl, f32x2 (&acc)[RW][M]) {
+            constexpr int SLOT = slot_bytes(kQ4_K);
+            X4 xa[M], xb[M];
+            f32x2 sx[M];
+#pragma unroll
+            for (int t = 0; t < M; ++t) {
+                xa[t] = lds_x4(xl + t * kSegCols * 4);
+                xb[t] = lds_x4(xl + (t * kSegCols + 32) * 4);
+                sx[t] = pack2(sum_x4(xa[t]), sum_x4(xb[t]));
+            }
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t w = lds32(wl + r * SLOT);
+                const uint32_t lo = w & 0x0F0F0F0Fu, hi = w & 0xF0F0F0F0u;
+                const ulonglong2 dl = lds128(el + r * 128);           // (dl, dl), (dl'/16, dl'/16), each times 2^64
+                const f32x2 nml = lds64(el + r * 128 + kPiece);      // (-ml, -ml') times 2^-77
+                // exact products (at most 21 significant bits): the dequantised weights without their minimum, times 2^-77
+                const f32x2 a01 = mul2(bytes_to_subpair<0, 1>(lo), dl.x), a23 = mul2(bytes_to_subpair<2, 3>(lo), dl.x);
+                const f32x2 b01 = mul2(bytes_to_subpair<0, 1>(hi), dl.y), b23 = mul2(bytes_to_subpair<2, 3>(hi), dl.y);
+#pragma unroll
+                for (int t = 0; t < M; ++t)
+                    acc[r][t] = fma2(nml, sx[t], fma2(b23, xb[t].p23, fma2(b01, xb[t].p01,
+                                fma2(a23, xa[t].p23, fma2(a01, xa[t].p01, acc[r][t])))));
+            }
+        }
+
         static __device__ __forceinline__ void go(uint32_t stage, uint32_t scratch, uint32_t xs, int nblk, f32x2 (&acc)[RW][M], int lane) {
             constexpr int SLOT = slot_bytes(kQ4_K);
             const f32x2 neg_magic = pack2(-8388608.0f, -8388608.0f);
@@ -39,7 +69,7 @@ struct Step<kQ4_K, M, RW> {
                 const int r = r0 + (lane >> 3), blk = (lane >> 1) & 3, hh = lane & 1;
                 if (r < NR) {
                     const uint4 h = lds128u(stage + r * SLOT + blk * 144);
-                    const float d = half_bits_to_float(h.x & 0xFFFFu), ndmin = -half_bits_to_float(h.x >> 16);
+                    const float d = half_bits_to_float(h.x & 0xFFFFu) * kSubScale, ndmin = -half_bits_to_float(h.x >> 16) * kSubWeight;
                     // four 6-bit fields at a time (engine/csrc/common/qwen_quant.cuh:78-86)
                     const uint32_t scw = hh ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
                     const uint32_t mnw = hh ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
@@ -57,36 +87,12 @@ struct Step<kQ4_K, M, RW> {
             const uint32_t xl = xs + (p * 64 + 4 * (lane & 7)) * 4;
             const uint32_t el = scratch + (p & 1) * 2 * kPiece + (p >> 1) * 16;
             const uint32_t wl = stage + 16 + 4 * lane;
+            if (nblk == 4) {  // a full segment: straight-line code
 #pragma unroll
-            for (int blk = 0; blk < 4; ++blk) {
-                if (blk < nblk) {
-                    X4 xa[M], xb[M];
-                    f32x2 sx[M];
-#pragma unroll
-                    for (int t = 0; t < M; ++t) {
-                        xa[t] = lds_x4(xl + (t * kSegCols + blk * 256) * 4);
-                        xb[t] = lds_x4(xl + (t * kSegCols + blk * 256 + 32) * 4);
-                        sx[t] = pack2(sum_x4(xa[t]), sum_x4(xb[t]));
-                    }
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) {
-                        const uint32_t w = lds32(wl + r * SLOT + blk * 144);
-                        const uint32_t lo = w & 0x0F0F0F0Fu, hi = w & 0xF0F0F0F0u;
-                        f32x2 a01 = bytes_to_pair<0, 1>(lo, neg_magic), a23 = bytes_to_pair<2, 3>(lo, neg_magic);
-                        f32x2 b01 = bytes_to_pair<0, 1>(hi, neg_magic), b23 = bytes_to_pair<2, 3>(hi, neg_magic);
-                        const ulonglong2 dl = lds128(el + (r * 4 + blk) * 32);           // (dl, dl), (dl'/16, dl'/16)
-                        const f32x2 nml = lds64(el + (r * 4 + blk) * 32 + kPiece);      // (-ml, -ml')
-                        // exact products (at most 21 significant bits): the dequantised weights without their minimum
-                        a01 = mul2(a01, dl.x);
-                        a23 = mul2(a23, dl.x);
-                        b01 = mul2(b01, dl.y);
-                        b23 = mul2(b23, dl.y);
-#pragma unroll
-                        for (int t = 0; t < M; ++t)
-                            acc[r][t] = fma2(nml, sx[t], fma2(b23, xb[t].p23, fma2(b01, xb[t].p01,
-                                        fma2(a23, xa[t].p23, fma2(a01, xa[t].p01, acc[r][t])))));
-                    }
-                }
+                for (int blk = 0; blk < 4; ++blk) block_dot(wl + blk * 144, el + blk * 32, xl + blk * 1024, acc);
+            } else {
+#pragma unroll 1
+                for (int blk = 0; blk < nblk; ++blk) block_dot(wl + blk * 144, el + blk * 32, xl + blk * 1024, acc);
             }
             __syncwarp();  // the scratch table is rewritten by the next step
         }
@@ -102,11 +108,15 @@ struct Step<kQ4_K, M, RW> {
 // Both share a block geometry: weight e = 128h + 32q + l (h: half, q: quarter, l < 32) takes its low bits from byte
 // 32h + l of a 64-byte plane (Q6_K: two planes of nibbles, Q3_K: one plane of 2-bit fields) and its high bits from a
 // second plane indexed by l, and weights 16k..16k+15 share sub-scale k = 8h + 2q + (l >> 4)
-// (engine/csrc/common/qwen_quant.cuh:182-190,199-210).  Neither carries a minimum.
-//   scale pass : lane -> (row, block, 4 sub-scales): integer sub-scale -> float, times d, stored as (dl, dl) pairs so
-//                that a dot-pass lane finds the sub-scales of its four quarters in one 32-byte slot [h][l >> 4][q].
-//   dot pass   : lane -> (block, half h, 4 consecutive l = 4j..4j+3): one word of each plane gives 16 weights, 4 per
-//                quarter, at columns 128h + 32q + 4j.  Eight lanes read 128 contiguous bytes of activations.
+// (engine/csrc/common/qwen_quant.cuh:182-190,199-210).  Neither carries a minimum; both subtract a constant bias.
+//   scale pass : lane -> (row, block, 4 sub-scales): integer sub-scale -> float, times d * 2^64, stored as (dl, dl)
+//                pairs so that a dot-pass lane finds the sub-scales of its four quarters in one 32-byte slot
+//                [h][l >> 4][q].
+//   dot pass   : lane -> (block, half h, 8 consecutive l = 8jj..8jj+7): two words of each plane give 32 weights, 8 per
+//                quarter, at columns 128h + 32q + 8jj, all eight under one sub-scale.  A quarter's fields are
+//                turned into subnormal floats f * 2^-141 and one FMA with (dl, c = -bias * dl * 2^-77) yields the
+//                dequantised weights times 2^-77 (exact).  Lanes with h = 1 take their second four columns first, so
+//                that the eight lanes of a 16-byte shared-memory load phase of activations touch 32 different banks.
 //                Blocks are only 2-byte aligned, so plane words are fetched with aligned loads + a funnel shift.
 template <int TYPE>
 struct QuarterFormat;
@@ -119,10 +129,18 @@ struct QuarterFormat<kQ6_K> {
     struct Words {
         uint32_t ql0, ql1, qh;
     };
-    static __device__ __forceinline__ Words load(uint32_t bp, int h, int j) {
-        return Words{lds32_a2(bp + 64 * h + 4 * j), lds32_a2(bp + 64 * h + 32 + 4 * j), lds32_a2(bp + 128 + 32 * h + 4 * j)};
+    // the lane's 8 bytes of the first nibble plane, and from there to its 8 bytes of the high-bit plane
+    static __device__ __forceinline__ uint32_t lane_off(int h, int jj) { return 64 * h + 8 * jj; }
+    static __device__ __forceinline__ uint32_t second_off(int h) { return 128 - 32 * h; }
+    // bf / bs: 4-byte aligned addresses at or below the lane's first / second four bytes of the first nibble plane,
+    // sh: 0 or 16 (the bytes start sh / 8 further)
+    static __device__ __forceinline__ void load(uint32_t bf, uint32_t bs, uint32_t sh, uint32_t d2nd, int, Words &first, Words &second) {
+        first = Words{__funnelshift_r(lds32(bf), lds32(bf + 4), sh), __funnelshift_r(lds32(bf + 32), lds32(bf + 36), sh),
+                      __funnelshift_r(lds32(bf + d2nd), lds32(bf + d2nd + 4), sh)};
+        second = Words{__funnelshift_r(lds32(bs), lds32(bs + 4), sh), __funnelshift_r(lds32(bs + 32), lds32(bs + 36), sh),
+                       __funnelshift_r(lds32(bs + d2nd), lds32(bs + d2nd + 4), sh)};
     }
-    // bytes = fields of quarter Q (4 weights), still carrying the bias
+    // bytes = fields of quarter Q (4 weights), still carrying the bias; every byte is below 0x80
     template <int Q>
     static __device__ __forceinline__ uint32_t quarter(const Words &w) {
         const uint32_t ql = (Q & 1) ? w.ql1 : w.ql0;
@@ -145,8 +163,12 @@ struct QuarterFormat<kQ3_K> {
     struct Words {
         uint32_t qs, hm;
     };
-    static __device__ __forceinline__ Words load(uint32_t bp, int h, int j) {
-        return Words{lds32_a2(bp + 32 + 32 * h + 4 * j), lds32_a2(bp + 4 * j) >> (4 * h)};
+    static __device__ __forceinline__ uint32_t lane_off(int h, int jj) { return 32 + 32 * h + 8 * jj; }
+    static __device__ __forceinline__ uint32_t second_off(int h) { return 0u - static_cast<uint32_t>(32 + 32 * h); }
+    static __device__ __forceinline__ void load(uint32_t bf, uint32_t bs, uint32_t sh, uint32_t d2nd, int h, Words &first, Words &second) {
+        // bit 4h + q of a mask byte belongs to quarter q of half h
+        first = Words{__funnelshift_r(lds32(bf), lds32(bf + 4), sh), __funnelshift_r(lds32(bf + d2nd), lds32(bf + d2nd + 4), sh) >> (4 * h)};
+        second = Words{__funnelshift_r(lds32(bs), lds32(bs + 4), sh), __funnelshift_r(lds32(bs + d2nd), lds32(bs + d2nd + 4), sh) >> (4 * h)};
     }
     template <int Q>
     static __device__ __forceinline__ uint32_t quarter(const Words &w) {
@@ -169,25 +191,41 @@ struct QuarterStep {
     using F = QuarterFormat<TYPE>;
     static constexpr int kEntry = 128;  // per (row, block): 16 sub-scales x (dl, dl), as [h][l >> 4][quarter]
     static constexpr int kScratch = RW * 4 * kEntry;
+    static constexpr float kOutScale = kSubOutScale;
 
     template <int NR>
     struct Pass {
-        template <int Q>
-        static __device__ __forceinline__ void quarter_dot(const typename F::Words (&w)[NR], uint32_t el, uint32_t xq, f32x2 neg_magic,
-                                                           f32x2 (&acc)[RW][M]) {
+        // Four of the lane's columns (xa: their activations) of one quarter, every row.
+        static __device__ __forceinline__ void quad_dot(const uint32_t (&q)[NR], const f32x2 (&d2)[NR], const f32x2 (&c2)[NR], uint32_t xa,
+                                                        f32x2 (&acc)[RW][M]) {
             X4 x[M];
 #pragma unroll
-            for (int t = 0; t < M; ++t) x[t] = lds_x4(xq + (t * kSegCols + Q * 32) * 4);
+            for (int t = 0; t < M; ++t) x[t] = lds_x4(xa + t * kSegCols * 4);
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
-                const uint32_t q = F::template quarter<Q>(w[r]);
-                f32x2 q01 = bytes_to_pair<0, 1>(q, neg_magic), q23 = bytes_to_pair<2, 3>(q, neg_magic);
-                const f32x2 d2 = lds64(el + r * 4 * kEntry + Q * 8);
-                q01 = mul2(q01, d2);  // exact: the dequantised weights
-                q23 = mul2(q23, d2);
+                // exact: field * 2^-141 * dl * 2^64 - bias * dl * 2^-77, the dequantised weight times 2^-77
+                const f32x2 q01 = fma2(bytes_to_subpair<0, 1>(q[r]), d2[r], c2[r]), q23 = fma2(bytes_to_subpair<2, 3>(q[r]), d2[r], c2[r]);
 #pragma unroll
                 for (int t = 0; t < M; ++t) acc[r][t] = fma2(q23, x[t].p23, fma2(q01, x[t].p01, acc[r][t]));
             }
+        }
+
+        template <int Q>
+        static __device__ __forceinline__ void quarter_dot(const typename F::Words (&first)[NR], const typename F::Words (&second)[NR],
+                                                           uint32_t el, uint32_t x_first, uint32_t x_second, f32x2 (&acc)[RW][M]) {
+            const f32x2 nbias = pack2(-F::kBias * 0x1p-141f, -F::kBias * 0x1p-141f);
+            uint32_t q[NR];
+            f32x2 d2[NR], c2[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                d2[r] = lds64(el + r * 4 * kEntry + Q * 8);
+                c2[r] = mul2(d2[r], nbias);
+                q[r] = F::template quarter<Q>(first[r]);
+            }
+            quad_dot(q, d2, c2, x_first + Q * 32 * 4, acc);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) q[r] = F::template quarter<Q>(second[r]);
+            quad_dot(q, d2, c2, x_second + Q * 32 * 4, acc);
         }
 
         static __device__ __forceinline__ void go(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t scratch, uint32_t xs, int nblk,
@@ -203,6 +241,7 @@ struct QuarterStep {
                         const uint32_t bp = stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB;
                         float d;
                         const uint32_t sw = F::scale_word(bp, c, &d);
+                        d *= kSubScale;
                         const f32x2 dd = pack2(d, d);
                         // sub-scale k = 4c + i belongs to half k >> 3, quarter (k >> 1) & 3, l >> 4 = k & 1
                         const uint32_t dst = scratch + (r * 4 + blk) * kEntry + (c >> 1) * 64 + (c & 1) * 16;
@@ -212,23 +251,23 @@ struct QuarterStep {
                 }
             }
             __syncwarp();
-            // ---- dot pass: a pass takes blocks s and s + 2
-            const f32x2 neg_magic = pack2(-(8388608.0f + F::kBias), -(8388608.0f + F::kBias));
-            const int bsel = lane >> 4, h = (lane >> 3) & 1, j = lane & 7;
+            // ---- dot pass: all four blocks at once
+            const int blk = lane >> 3, h = (lane >> 2) & 1, jj = lane & 3;
+            if (blk < nblk) {
+                const uint32_t lane_off = blk * BB + F::lane_off(h, jj), d2nd = F::second_off(h);
+                typename F::Words first[NR], second[NR];
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
-                const int blk = s + 2 * bsel;
-                if (blk < nblk) {
-                    typename F::Words w[NR];
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) w[r] = F::load(stage + r * SLOT + ((d0 + r * rb16) & 15u) + blk * BB, h, j);
-                    const uint32_t el = scratch + blk * kEntry + (h * 2 + (j >> 2)) * 32;
-                    const uint32_t xq = xs + (blk * 256 + h * 128 + 4 * j) * 4;
-                    quarter_dot<0>(w, el, xq, neg_magic, acc);
-                    quarter_dot<1>(w, el, xq, neg_magic, acc);
-                    quarter_dot<2>(w, el, xq, neg_magic, acc);
-                    quarter_dot<3>(w, el, xq, neg_magic, acc);
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t a = stage + r * SLOT + ((d0 + r * rb16) & 15u) + lane_off, b = a & ~3u;
+                    F::load(b + 4 * h, b + 4 - 4 * h, (a & 2u) << 3, d2nd, h, first[r], second[r]);
                 }
+                const uint32_t el = scratch + blk * kEntry + (h * 2 + (jj >> 1)) * 32;
+                const uint32_t x_first = xs + (blk * 256 + 128 * h + 8 * jj + 4 * h) * 4;
+                const uint32_t x_second = xs + (blk * 256 + 128 * h + 8 * jj + 4 * (1 - h)) * 4;
+                quarter_dot<0>(first, second, el, x_first, x_second, acc);
+                quarter_dot<1>(first, second, el, x_first, x_second, acc);
+                quarter_dot<2>(first, second, el, x_first, x_second, acc);
+                quarter_dot<3>(first, second, el, x_first, x_second, acc);
             }
             __syncwarp();  // the scratch table is rewritten by the next step
         }
