@@ -245,27 +245,45 @@ def run_gpu(args) -> None:
     for w in widths:
         rt.bind(f"x{w}", dev_x[w].data_ptr(), m * w)
         dev_x[w].copy_(host_x[w].view(-1))
-    out_rows = sorted({rows for _, _, rows, _ in tensors})
+    def kind_of(name: str) -> str:
+        return name.split(".")[-1]
 
     def slice_rows(r: int, k: int) -> int:
         b, e = shard_rows(r, k, world)
         return e - b
 
-    # per output width: this rank's [M][rows of the slice] block, padded to the widest slice so that one
-    # all_gather_into_tensor of equal-sized chunks combines the ranks
-    widest = {r: max(slice_rows(r, k) for k in range(world)) for r in out_rows}
-    y_local = {r: torch.zeros(m * widest[r], dtype=torch.float32, device=dev) for r in out_rows}
-    for r in out_rows:
-        rt.bind(f"y{r}", y_local[r].data_ptr(), m * slice_rows(r, rank))
-    gathered = {r: torch.empty(world * m * widest[r], dtype=torch.float32, device=dev) for r in out_rows} if world > 1 else {}
+    # per kind of tensor: this rank's [M][rows of the slice] block, padded to the widest slice so that one
+    # all_gather_into_tensor of equal-sized chunks combines the ranks (NCCL arm)
+    kind_rows = {kind_of(name): rows for name, _, rows, _ in tensors}
+    widest = {k: max(slice_rows(r, i) for i in range(world)) for k, r in kind_rows.items()}
+    y_local = {k: torch.zeros(m * widest[k], dtype=torch.float32, device=dev) for k in kind_rows}
+    for k, r in kind_rows.items():
+        rt.bind(f"y.{k}", y_local[k].data_ptr(), m * slice_rows(r, rank))
+    gathered = {k: torch.empty(world * m * widest[k], dtype=torch.float32, device=dev) for k in kind_rows} if world > 1 else {}
     ids_addr, vals_addr = rt.argmax_result()
     torch.cuda.synchronize()
 
+    # The launches of a pass.  Tensors that read the same activations and share type and columns go out as ONE launch
+    # (q/k/v, gate/up) unless --launches per-tensor asks for the reference's one kernel per tensor.
+    GROUPS = {"attn_q": 0, "attn_k": 0, "attn_v": 0, "attn_o": 1, "ffn_gate": 2, "ffn_up": 2, "ffn_down": 3, "output": 4}
+    launches_of_pass: list[list[tuple[str, T, int, int]]] = []
+    for entry in tensors:
+        layer, g = entry[0].rsplit(".", 1)[0], GROUPS[kind_of(entry[0])]
+        if args.launches == "grouped" and launches_of_pass and launches_of_pass[-1][0][0].rsplit(".", 1)[0] == layer and \
+                GROUPS[kind_of(launches_of_pass[-1][0][0])] == g:
+            launches_of_pass[-1].append(entry)
+        else:
+            launches_of_pass.append([entry])
+
     def enqueue_pass() -> None:
-        for name, t, rows, cols in tensors[:-1]:
-            rt.qmv(name, f"x{cols}", f"y{rows}", m)
-        name, t, rows, cols = tensors[-1]
-        rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
+        for group in launches_of_pass[:-1]:
+            cols = group[0][3]
+            if len(group) == 1:
+                rt.qmv(group[0][0], f"x{cols}", f"y.{kind_of(group[0][0])}", m)
+            else:
+                rt.qmv_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m)
+        name, t, rows, cols = launches_of_pass[-1][0]
+        rt.qmv_argmax(name, f"x{cols}", f"y.{kind_of(name)}", m, blocking=False)
 
     # single GPU: the whole pass is one CUDA graph; multi GPU: kernels on the runtime's stream, gathers after each
     graph = None
@@ -276,13 +294,18 @@ def run_gpu(args) -> None:
         enqueue_pass()
         graph = rt.capture_end()
 
-    def sharded_pass() -> None:  # NCCL arm: kernel, all-gather, kernel, ... launched eagerly
-        for name, t, rows, cols in tensors[:-1]:
-            rt.qmv(name, f"x{cols}", f"y{rows}", m)
-            dist.all_gather_into_tensor(gathered[rows], y_local[rows])
-        name, t, rows, cols = tensors[-1]
-        rt.qmv_argmax(name, f"x{cols}", f"y{rows}", m, blocking=False)
-        dist.all_gather_into_tensor(gathered[rows], y_local[rows])
+    def sharded_pass() -> None:  # NCCL arm: kernel, all-gather(s), kernel, ... launched eagerly
+        for group in launches_of_pass[:-1]:
+            cols = group[0][3]
+            if len(group) == 1:
+                rt.qmv(group[0][0], f"x{cols}", f"y.{kind_of(group[0][0])}", m)
+            else:
+                rt.qmv_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m)
+            for e in group:
+                dist.all_gather_into_tensor(gathered[kind_of(e[0])], y_local[kind_of(e[0])])
+        name, t, rows, cols = launches_of_pass[-1][0]
+        rt.qmv_argmax(name, f"x{cols}", f"y.{kind_of(name)}", m, blocking=False)
+        dist.all_gather_into_tensor(gathered[kind_of(name)], y_local[kind_of(name)])
 
     # Fused arm (default): every matvec pushes its slice into the gathered vector of every rank from its own epilogue and
     # the next matvec waits for all ranks' flags - the dependency chain of a tensor-parallel decoder.  One gathered
@@ -296,29 +319,38 @@ def run_gpu(args) -> None:
         kinds = {}
         off = 0
         for name, t, rows, cols in tensors:
-            kind = name.split(".")[-1]
-            if kind not in kinds:
-                kinds[kind] = off
+            if kind_of(name) not in kinds:
+                kinds[kind_of(name)] = off
                 off += (4 * m * rows + 255) // 256 * 256
-        layout = ExchangeLayout(off, n_slots=len(tensors))
+        layout = ExchangeLayout(off, n_slots=len(launches_of_pass))
         connect_exchange(rt, layout)
 
         # the launch whose flags a launch waits for: the last one that produced (part of) its input
-        producer_kind = {"attn_q": "ffn_down", "attn_k": "ffn_down", "attn_v": "ffn_down", "attn_o": "attn_v", "ffn_gate": "attn_o",
-                         "ffn_up": "attn_o", "ffn_down": "ffn_up", "output": "ffn_down"}
+        producer_kind = {"attn_q": "ffn_down", "attn_o": "attn_v", "ffn_gate": "attn_o", "ffn_up": "attn_o", "ffn_down": "ffn_up",
+                         "output": "ffn_down"}
         last_of_kind: dict[str, int] = {}
         wait_for = []
-        for i, (name, t, rows, cols) in enumerate(tensors):
-            wait_for.append(last_of_kind.get(producer_kind[name.split(".")[-1]], len(tensors) - 1))  # first layer: previous pass's last launch
-            last_of_kind[name.split(".")[-1]] = i
+        for i, group in enumerate(launches_of_pass):
+            lead = kind_of(group[0][0])
+            wait_for.append(last_of_kind.get(producer_kind.get(lead, "ffn_down"), len(launches_of_pass) - 1))  # first layer: previous pass's last launch
+            for e in group:
+                last_of_kind[kind_of(e[0])] = i
 
         def push_pass() -> None:
             rt.exchange_next_pass()
-            for i, (name, t, rows, cols) in enumerate(tensors):
-                b, e = local_rows[name]
-                rt.qmv_push(name, f"x{cols}", f"y{rows}", m, slot=i if push_mode != "none" else -1, dst_off=kinds[name.split(".")[-1]],
-                            rows_total=rows, row_begin=b, wait_slot=wait_for[i] if push_mode == "full" else -1,
-                            wait_lag=1 if wait_for[i] >= i else 0, with_argmax=(i == len(tensors) - 1))
+            for i, group in enumerate(launches_of_pass):
+                cols = group[0][3]
+                slot = i if push_mode != "none" else -1
+                wait_slot = wait_for[i] if push_mode == "full" else -1
+                lag = 1 if wait_for[i] >= i else 0
+                if len(group) == 1:
+                    name, t, rows, _ = group[0]
+                    rt.qmv_push(name, f"x{cols}", f"y.{kind_of(name)}", m, slot=slot, dst_off=kinds[kind_of(name)], rows_total=rows,
+                                row_begin=local_rows[name][0], wait_slot=wait_slot, wait_lag=lag, with_argmax=(i == len(launches_of_pass) - 1))
+                else:
+                    rt.qmv_push_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m, slot=slot,
+                                      dst_offs=[kinds[kind_of(e[0])] for e in group], rows_totals=[e[2] for e in group],
+                                      row_begins=[local_rows[e[0]][0] for e in group], wait_slot=wait_slot, wait_lag=lag)
 
         push_pass()
         rt.synchronize()
@@ -382,7 +414,7 @@ def run_gpu(args) -> None:
     ms = timed(device_pass, args.steps)
     launches = rt.launch_count() - launches_before
     if torch_graph is not None:
-        launches = args.steps * len(tensors)  # replayed by torch's graph, not counted by the runtime
+        launches = args.steps * len(launches_of_pass)  # replayed by torch's graph, not counted by the runtime
     e2e_ms = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else {}
 
@@ -392,7 +424,7 @@ def run_gpu(args) -> None:
 
     def dominant() -> None:
         for name, t, rows, cols in dom:
-            rt.qmv(name, f"x{cols}", f"y{rows}", m)
+            rt.qmv(name, f"x{cols}", f"y.{kind_of(name)}", m)
 
     dominant()
     dom_ms = timed(dominant, max(2, args.steps // 2)) / len(dom)
@@ -410,7 +442,7 @@ def run_gpu(args) -> None:
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"synthetic-27B decode pass, M={m}: 64 x (Q6_K q/k/v/o, Q3_K gate/up, Q4_K down) + Q6_K LM head 151936x5120 "
                                    f"with fused argmax; {weight_bytes_total} weight bytes resident in HBM", "activation_rows": m,
-                       "launches_per_pass": len(tensors), "l2": "pass is ~100x larger than L2 (no flush needed)",
+                       "launches_per_pass": len(launches_of_pass), "launches": args.launches, "l2": "pass is ~100x larger than L2 (no flush needed)",
                        "parallelism": "single GPU, one CUDA graph per pass" if world == 1 else (f"output rows sharded over {world} GPUs; every matvec pushes its slice into all ranks' gathered vector over NVLink from its epilogue "
                                         "and waits for the flags of the launch that produced its input (decoder dependency chain); one CUDA graph per rank, no collective" if use_push else
                                         f"output rows sharded over {world} GPUs, NCCL all-gather after every matvec, eager launches")},
@@ -441,6 +473,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--m", type=int, default=4, help="activation rows per pass (1..8)")
+    ap.add_argument("--launches", default="grouped", choices=["grouped", "per-tensor"],
+                    help="grouped: q/k/v and gate/up of a layer go out as one launch each; per-tensor: one kernel per tensor, as the reference launches")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
                     help="multi-GPU: how output slices are combined - fused peer-memory push from the kernel (default) or NCCL all-gather")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline leg (0 = skip)")

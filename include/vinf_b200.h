@@ -180,6 +180,23 @@ int vqm_exchange_next_pass(vqm_runtime *rt);
 int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int slot, size_t dst_off, int rows_total,
                  int row_begin, int wait_slot, int wait_lag, int with_argmax);
 
+/* ---- Several tensors in one launch (no counterpart in the reference, which launches one kernel per tensor) ----
+ * Tensors that read the same activations, share their GGUF type and have the same number of columns - the q/k/v
+ * projections of an attention layer, the gate/up pair of an FFN - can be run by ONE launch: ys[i] = W_i x.  The
+ * launch treats their rows as one list, so short tensors ride along with long ones instead of paying for a launch
+ * each.  Every output equals, bit for bit, what vqm_qmv gives for its tensor alone, unless one of the two launches
+ * is short enough to be split by columns (a launch whose rows would leave more than half of the GPU's warps idle
+ * shares each row's columns among up to 8 blocks and adds their partial sums in column order; the grouping of the
+ * additions then depends on the number of rows in the launch, never on ntok).
+ *   n: 1..4 tensors; ntok: 1..8.  VQM_ERR_VALUE if the tensors do not share type and columns, or if a tensor's rows
+ *   cannot follow the previous tensor's in one launch (for types whose rows are not multiples of 16 bytes, the row
+ *   counts of all but the last tensor have to keep the rows' position within a 16-byte line going).
+ * vqm_qmv_push_group is the row-sharded form (see vqm_qmv_push): per tensor its place in the gathered vectors, one
+ * flag slot for the whole launch. */
+int vqm_qmv_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok);
+int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok, int slot,
+                       const size_t *dst_offs, const int *rows_totals, const int *row_begins, int wait_slot, int wait_lag);
+
 /* No counterpart in the reference.  The LM-head matvec with fused argmax (like vqm_qmv_argmax) for callers that
  * must not allocate device memory - code inside a no-allocation region of a serving loop, a process whose GPU
  * memory was all handed out at start-up, a plugin limited to the buffers its host gave it.  Stateless: the caller

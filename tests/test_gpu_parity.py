@@ -380,3 +380,94 @@ def test_prompt_gemm_larger_shapes_and_threshold(rt, clib, codebooks, t, rows, c
     assert rel_l2(small, ref[:8]) <= REL_L2
     with pytest.raises(ValueError):
         rt.set_gemm_min_rows(-1)
+
+
+# ---- several tensors in one launch; short launches split by columns ------------------------------------------
+
+def _upload_group(rt, t, shapes, cols, ntok, rng):
+    raws = []
+    for i, rows in enumerate(shapes):
+        raw = synthetic_blocks(t, rows, cols, rng)
+        rt.upload(f"g{i}", raw, int(t), cols, rows)
+        rt.alloc(f"gy{i}", ntok * rows)
+        rt.alloc(f"sy{i}", ntok * rows)
+        raws.append(raw)
+    return raws
+
+
+@pytest.mark.parametrize("t,shapes,ntok", [(T.Q6_K, (1538, 258, 256), 4), (T.Q3_K, (2048, 2050), 1), (T.Q4_K, (1301, 77, 300, 5), 8),
+                                            (T.IQ4_XS, (1400, 3), 3), (T.IQ3_S, (1500, 700), 2)], ids=lambda v: getattr(v, "name", str(v)))
+def test_group_launch_equals_one_launch_per_tensor_bit_for_bit(rt, codebooks, t, shapes, ntok):
+    """q/k/v-like and gate/up-like groups: one launch over all rows gives every tensor exactly what its own launch
+    gives (1024 columns: a single column segment, so neither launch can be split by columns)."""
+    rng = np.random.default_rng(sum(shapes) + ntok)
+    cols = 1024
+    raws = _upload_group(rt, t, shapes, cols, ntok, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    rt.alloc("x", ntok * cols)
+    rt.write("x", x)
+    n = len(shapes)
+    rt.qmv_group([f"g{i}" for i in range(n)], "x", [f"gy{i}" for i in range(n)], ntok)
+    for i in range(n):
+        rt.qmv(f"g{i}", "x", f"sy{i}", ntok)
+    rt.synchronize()
+    for i, rows in enumerate(shapes):
+        grouped = rt.read_array(f"gy{i}", ntok * rows)
+        assert np.array_equal(grouped.view(np.uint32), rt.read_array(f"sy{i}", ntok * rows).view(np.uint32)), i
+        ref = O.matvec(raws[i], int(t), rows, cols, x, codebooks)
+        assert rel_l2(grouped.reshape(ntok, rows), ref) <= REL_L2
+
+
+@pytest.mark.parametrize("t,shapes,cols,ntok", [(T.Q6_K, (768, 128, 128), 5120, 4), (T.Q4_K, (640,), 17408, 4), (T.Q3_K, (90, 30), 3072, 8),
+                                                 (T.Q6_K, (9,), 5120, 1), (T.IQ2_S, (400, 200), 2304, 2), (T.Q8_0, (1184,), 2048, 3)],
+                         ids=lambda v: getattr(v, "name", str(v)))
+def test_short_launches_split_by_columns_match_the_oracle(rt, clib, codebooks, t, shapes, cols, ntok):
+    """Row shards of an 8-GPU split and other short launches: the rows' columns are shared among several blocks whose
+    partial sums are added in column order.  Same tolerance as everywhere, and an M-row pass still equals M single-row
+    passes bit for bit."""
+    rng = np.random.default_rng(sum(shapes) + cols + ntok)
+    raws = _upload_group(rt, t, shapes, cols, ntok, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    rt.alloc("x", ntok * cols)
+    rt.alloc("x1", cols)
+    rt.write("x", x)
+    n = len(shapes)
+    names, outs = [f"g{i}" for i in range(n)], [f"gy{i}" for i in range(n)]
+    rt.qmv_group(names, "x", outs, ntok)
+    rt.synchronize()
+    got = [rt.read_array(f"gy{i}", ntok * rows).reshape(ntok, rows).copy() for i, rows in enumerate(shapes)]
+    for i, rows in enumerate(shapes):
+        ref = oracle_libs.c_qmv(clib, raws[i], int(t), rows, cols, x, codebooks)
+        assert rel_l2(got[i], ref) <= REL_L2, i
+    for k in range(ntok):
+        rt.write("x1", x[k])
+        rt.qmv_group(names, "x1", outs, 1)
+        rt.synchronize()
+        for i, rows in enumerate(shapes):
+            assert np.array_equal(rt.read_array(f"gy{i}", rows).view(np.uint32), got[i][k].view(np.uint32)), (i, k)
+
+
+def test_group_launch_error_contract(rt):
+    rng = np.random.default_rng(5)
+    rt.upload("ga", synthetic_blocks(T.Q6_K, 7, 256, rng), int(T.Q6_K), 256, 7)   # 7 rows of 210 bytes: the next tensor's rows
+    rt.upload("gb", synthetic_blocks(T.Q6_K, 8, 256, rng), int(T.Q6_K), 256, 8)   # would start at byte 14 of a 16-byte line, not at 0
+    rt.upload("gc", synthetic_blocks(T.Q4_K, 8, 256, rng), int(T.Q4_K), 256, 8)
+    rt.upload("gd", synthetic_blocks(T.Q6_K, 8, 512, rng), int(T.Q6_K), 512, 8)
+    for name, n in (("x", 8 * 512), ("ya", 64), ("yb", 64), ("small", 4)):
+        rt.alloc(name, n)
+    rt.qmv_group(["gb", "ga"], "x", ["yb", "ya"], 2)  # 8 rows first: fine
+    rt.synchronize()
+    with pytest.raises(ValueError):
+        rt.qmv_group(["ga", "gb"], "x", ["ya", "yb"], 2)
+    with pytest.raises(ValueError):
+        rt.qmv_group(["gb", "gc"], "x", ["ya", "yb"], 1)  # types differ
+    with pytest.raises(ValueError):
+        rt.qmv_group(["gb", "gd"], "x", ["ya", "yb"], 1)  # columns differ
+    with pytest.raises(ValueError):
+        rt.qmv_group(["gb"] * 5, "x", ["ya"] * 5, 1)
+    with pytest.raises(ValueError):
+        rt.qmv_group(["gb"], "x", ["small"], 1)
+    with pytest.raises(KeyError):
+        rt.qmv_group(["gb", "nope"], "x", ["ya", "yb"], 1)
+    with pytest.raises(ValueError):
+        rt.qmv_group(["gb"], "x", ["ya"], 9)

@@ -75,6 +75,35 @@ def test_push_gathers_slices_on_every_rank_and_chains(two_ranks, codebooks):
         assert rel_l2(rt.read_array("gathered2").reshape(m, rows2), ref2) <= 1e-5
 
 
+def test_push_of_a_group_launch_fills_both_gathered_vectors(two_ranks, codebooks):
+    """Two tensors that share x in one launch per rank (q/k-like), short enough to be split by columns as well: each
+    tensor's slice lands in its own gathered vector on every rank, one flag slot covers the launch."""
+    rts, layout, (m, rows, cols, rows2) = two_ranks
+    rng = np.random.default_rng(14)
+    cols = 2048
+    raw_a, raw_b = synthetic_blocks(T.Q6_K, rows, cols, rng), synthetic_blocks(T.Q6_K, rows2, cols, rng)
+    x = synthetic_activations(m, cols, rng)
+    ref_a, ref_b = O.matvec(raw_a, int(T.Q6_K), rows, cols, x, codebooks), O.matvec(raw_b, int(T.Q6_K), rows2, cols, x, codebooks)
+    for rank, rt in enumerate(rts):
+        (ba, ea), (bb, eb) = shard_rows(rows, rank, 2), shard_rows(rows2, rank, 2)
+        rt.upload("wa", raw_a[ba:ea], int(T.Q6_K), cols, ea - ba)
+        rt.upload("wb", raw_b[bb:eb], int(T.Q6_K), cols, eb - bb)
+        rt.alloc("x", m * cols)
+        rt.alloc("ya", m * (ea - ba))
+        rt.alloc("yb", m * (eb - bb))
+        rt.write("x", x)
+        rt.exchange_next_pass()
+        rt.qmv_push_group(["wa", "wb"], "x", ["ya", "yb"], m, slot=0, dst_offs=[0, 4 * m * rows], rows_totals=[rows, rows2],
+                          row_begins=[ba, bb])
+        rt.synchronize()
+        assert rel_l2(rt.read_array("ya").reshape(m, ea - ba), ref_a[:, ba:ea]) <= 1e-5
+    for rt in rts:
+        assert rel_l2(rt.read_array("gathered").reshape(m, rows), ref_a) <= 1e-5
+        assert rel_l2(rt.read_array("gathered2").reshape(m, rows2), ref_b) <= 1e-5
+        flags = np.frombuffer(rt.read("flags"), dtype=np.uint32).reshape(layout.n_slots, 8)
+        assert list(flags[0, :2]) == [1, 1]
+
+
 def test_push_with_fused_argmax_reports_global_rows(two_ranks, codebooks):
     rts, layout, (m, rows, cols, rows2) = two_ranks
     rng = np.random.default_rng(12)

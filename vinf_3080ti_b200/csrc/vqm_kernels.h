@@ -7,39 +7,60 @@
 
 namespace vqm {
 
+constexpr int kMaxParts = 4;  // tensors one launch can cover (they share the activations, the type and the columns)
+
 // Row-sharded matvec across GPUs: where a launch stores its outputs inside every rank's exchange region (plain remote
 // stores over NVLink, issued by the lane that holds the output) and which flags order that against the consumers.
 struct PushInfo {
     unsigned long long region[8];  // device address of every rank's exchange region, this rank's included
     const unsigned *epoch;         // this rank's pass counter (device memory, advanced once per pass)
-    long long dst_off;             // byte offset, inside a region, of the gathered y[0][0] of this launch
+    long long dst_off[kMaxParts];  // per tensor: byte offset, inside a region, of its gathered y[0][0]
     long long flag_off;            // byte offset, inside a region, of the flag table: unsigned flags[slot][8 ranks]
     int n_ranks, rank;
-    int rows_total, row_begin;     // the gathered tensor has rows_total rows; this rank's slice starts at row_begin
+    int rows_total[kMaxParts];     // per tensor: the gathered tensor has rows_total rows ...
+    int row_begin[kMaxParts];      // ... and this rank's slice starts at row_begin
     int push_slot;                 // 1 + flag slot signalled after the push (0: no push)
     int wait_slot;                 // 1 + flag slot every rank must have signalled before x is read (0: no wait)
     int wait_lag;                  // the wait is for epoch - wait_lag (1: the slot was signalled in the previous pass)
 };
 
+// One tensor of a launch.  The launch numbers the rows of its tensors consecutively; tensor p owns launch rows
+// [row_end of tensor p - 1, row_end).  Unused entries have row_end = INT_MAX.
+struct MatvecPart {
+    const uint8_t *w;  // raw blocks, readable up to 15 bytes past the end
+    float *y;          // [M][rows] fp32 (may be null when only the argmax is wanted)
+    int row_end;
+    int rows;          // rows of this tensor (the stride of y)
+};
+
 struct MatvecArgs {
-    const uint8_t *w;        // raw blocks, 16-byte aligned, readable up to 15 bytes past the end
+    MatvecPart part[kMaxParts];
     const float *x;          // [M][cols] fp32, 16-byte aligned
-    float *y;                // [M][rows] fp32 (may be null when only the argmax is wanted)
     const uint8_t *codebook;  // device copy of the type's GGUF codebook (IQ2/IQ3 types), else null
     unsigned *status;        // device error word (0 = fine)
-    // fused argmax (all null / 0 when unused)
+    // fused argmax (all null / 0 when unused; single-tensor launches only)
     float *part_val;         // [kMaxTok][gridDim.x]
     int *part_idx;           // [kMaxTok][gridDim.x]
     unsigned *done_counter;  // zero before the launch; the kernel leaves it zero
     int *out_idx;            // [M] winning row (+ row_base), 0x7fffffff if the column has no value above -inf
     float *out_val;          // [M] winning value (may be null)
-    int rows, cols;
+    int rows, cols;          // rows: of all tensors together
     long long row_bytes;
     int row_base;            // added to row numbers reported by the argmax (row-sharded weights)
+    // Column split for short launches: k_split blocks share a group of rows, each takes a range of the column segments
+    // and leaves partial sums in split_partial[k][M][rows]; the last of them to finish adds the partials in the order
+    // of k and writes the outputs.  split_counters: one per row group, zero between launches.
+    int k_split;             // chosen by the launcher (from the rows and the columns only, never from M); 1 = off
+    float *split_partial;    // null: never split
+    unsigned *split_counters;
+    int split_capacity;      // floats in split_partial
     int overlap_launch;      // host only: launch with programmatic stream serialization (see qmv_kernel)
     int max_grid;            // host only: upper bound on the grid (0 = none); sizes the argmax partial arrays
     PushInfo push;           // all zero when the tensor is not sharded
 };
+
+constexpr int kMaxSplit = 8;          // column ranges a row can be split into
+constexpr int kSplitGroups = 4096;    // row groups a split launch can have (size of split_counters)
 
 enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1, kStatusPeerWaitExpired = 2 };
 

@@ -59,28 +59,29 @@ __host__ __device__ constexpr size_t matvec_smem_bytes(int type, int rw, int m) 
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+// (barriers and staging buffers are named by their 32-bit shared-space addresses)
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
 
 // Bounded wait: ~2^22 polls with a short sleep after the first few hundred.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
 #pragma unroll 1
     for (int i = 0; i < (1 << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -91,10 +92,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
 
 // One contiguous global -> shared copy of `bytes` (multiple of 16; both addresses 16-byte aligned),
 // completion counted in bytes on `bar`.  No multicast.
-__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(bar)
                  : "memory");
 }
 
@@ -106,6 +106,35 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
+// Where launch row g lives: the tensor's output vector and the row inside the tensor, plus the tensor's place in the
+// gathered vectors of a row-sharded launch.  A chain of selects over the (at most kMaxParts) tensors; kernel
+// parameters are only indexed with constants.
+struct RowHome {
+    float *y;
+    int local, rows, rows_total, row_begin;
+    long long dst_off;
+};
+__device__ __forceinline__ RowHome home_of(const MatvecArgs &a, int g) {
+    RowHome h{a.part[0].y, g, a.part[0].rows, a.push.rows_total[0], a.push.row_begin[0], a.push.dst_off[0]};
+#pragma unroll
+    for (int i = 1; i < kMaxParts; ++i)
+        if (g >= a.part[i - 1].row_end) h = RowHome{a.part[i].y, g - a.part[i - 1].row_end, a.part[i].rows, a.push.rows_total[i],
+                                                     a.push.row_begin[i], a.push.dst_off[i]};
+    return h;
+}
+// Address of the first byte of launch row g.
+__device__ __forceinline__ uintptr_t row_address(const MatvecArgs &a, int g) {
+    const uint8_t *w = a.part[0].w;
+    int local = g;
+#pragma unroll
+    for (int i = 1; i < kMaxParts; ++i)
+        if (g >= a.part[i - 1].row_end) {
+            w = a.part[i].w;
+            local = g - a.part[i - 1].row_end;
+        }
+    return reinterpret_cast<uintptr_t>(w) + static_cast<uintptr_t>(local) * static_cast<uintptr_t>(a.row_bytes);
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------------
 
 template <int TYPE, int RW, int M>
@@ -113,11 +142,13 @@ __host__ __device__ constexpr size_t matvec_smem_bytes_for() {
     return matvec_smem_bytes(TYPE, RW, M) + static_cast<size_t>(kWarps) * Step<TYPE, M, RW>::kScratch;
 }
 
+// Blocks per SM the register allocation aims for: two, except for the tall chunks of wide passes (their sums alone
+// take RW * M register pairs).  One-row chunks always get two, which the column split of short launches counts on.
 #ifndef VQM_MIN_BLOCKS
-#define VQM_MIN_BLOCKS(M) ((M) <= 4 ? 2 : 1)
+#define VQM_MIN_BLOCKS(M, RW) (((M) <= 4 || (RW) == 1) ? 2 : 1)
 #endif
 template <int TYPE, int M, int RW>
-__global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(const MatvecArgs a) {
+__global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel(const MatvecArgs a) {
     using StepT = Step<TYPE, M, RW>;
     constexpr int S = stages_for(TYPE, RW);
     constexpr int XS = x_stages_for(M);
@@ -130,24 +161,26 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
     static_assert(kWarps * 8 * 8 + 8 * 8 + 8 * 4 <= kBarrierBytes, "barrier area");
 
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t *table = smem;
-    uint64_t *wbars = reinterpret_cast<uint64_t *>(smem + TABLE);          // [kWarps][8] weight stages
-    uint64_t *xfull = wbars + kWarps * 8;                                    // [XS] activation stages
-    int *xdone = reinterpret_cast<int *>(xfull + 8);                         // [XS] warps done with the stage
-    uint8_t *xbuf = smem + TABLE + kBarrierBytes;
+    // layout: lookup table | barriers: [kWarps][8] weight stages, [8] activation stages, [XS] "warps done" counters |
+    //         XS activation stages | per warp S x RW weight slots | per warp decoder scratch
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint64_t *bar = wbars + warp * 8;
-    uint8_t *buf = xbuf + XS * XSTAGE + static_cast<size_t>(warp) * (S * RW * SLOT);
-    uint8_t *scratch = xbuf + XS * XSTAGE + static_cast<size_t>(kWarps) * (S * RW * SLOT) + warp * StepT::kScratch;
+    const uint32_t smem0 = smem_u32(smem);
+    uint8_t *table = smem;
+    int *xdone = reinterpret_cast<int *>(smem + TABLE + (kWarps * 8 + 8) * 8);
+    const uint32_t xfull = smem0 + TABLE + kWarps * 8 * 8;
+    const uint32_t xbuf = smem0 + TABLE + kBarrierBytes;
+    const uint32_t bar = smem0 + TABLE + warp * 64;
+    const uint32_t buf = xbuf + XS * XSTAGE + warp * (S * RW * SLOT);
+    const uint32_t scratch = xbuf + XS * XSTAGE + kWarps * (S * RW * SLOT) + warp * StepT::kScratch;
 
     if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < S; ++s) mbar_init(bar + s, 1);
+        for (int s = 0; s < S; ++s) mbar_init(bar + s * 8, 1);
     }
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int s = 0; s < XS; ++s) {
-            mbar_init(xfull + s, 1);
+            mbar_init(xfull + s * 8, 1);
             xdone[s] = 0;
         }
     }
@@ -155,46 +188,50 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
-    // Even split of the rows over all warps of the grid: warp gw gets `my_count` consecutive rows from
-    // `my_begin`, taken in `n_chunks` chunks of at most RW rows (chunk sizes differ by at most one).
-    // n_chunks is the same for every warp, so the warps of a block share the activation stages.
-    const int total_warps = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
+    // Even split of the rows over the warps: warp gw gets `my_count` consecutive rows from `my_begin`, taken in
+    // `n_chunks` chunks of at most RW rows (chunk sizes differ by at most one).  n_chunks is the same for every warp,
+    // so the warps of a block share the activation stages.  With a column split, k_split consecutive blocks form a
+    // group that shares its rows and block `kpart` of the group takes column segments [seg_begin, seg_begin + n_seg).
+    const int k_split = a.k_split, n_groups = gridDim.x / k_split, group = blockIdx.x / k_split, kpart = blockIdx.x % k_split;
+    const int total_warps = n_groups * kWarps, gw = group * kWarps + warp;
     const int base = a.rows / total_warps, rem = a.rows % total_warps;
     const int my_count = base + (gw < rem ? 1 : 0), my_begin = gw * base + (gw < rem ? gw : rem);
     const int n_chunks = (base + (rem > 0 ? 1 : 0) + RW - 1) / RW;
     const int chunk_base = my_count / n_chunks, chunk_rem = my_count % n_chunks;  // chunk c has chunk_base + (c < chunk_rem) rows
-    const int n_seg = (a.cols + kSegCols - 1) / kSegCols;
+    const int n_seg_all = (a.cols + kSegCols - 1) / kSegCols;
+    const int seg_begin = kpart * n_seg_all / k_split, n_seg = (kpart + 1) * n_seg_all / k_split - seg_begin;
     const int n_steps = n_chunks * n_seg;
-    const uintptr_t wbase = reinterpret_cast<uintptr_t>(a.w);
+    const uint32_t w_align = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(a.part[0].w) & 15u);
     const uint32_t rb16 = static_cast<uint32_t>(a.row_bytes) & 15u;
 
     // Activation stage for step `step` (segment `seg`): one bulk copy per activation row.  Called by one thread.
     auto issue_x = [&](int xstage, int seg) {
         const int cols_here = a.cols - seg * kSegCols < kSegCols ? a.cols - seg * kSegCols : kSegCols;
-        mbar_expect_tx(xfull + xstage, static_cast<uint32_t>(M * cols_here * 4));
+        mbar_expect_tx(xfull + xstage * 8, static_cast<uint32_t>(M * cols_here * 4));
 #pragma unroll
         for (int t = 0; t < M; ++t)
             bulk_copy_g2s(xbuf + xstage * XSTAGE + t * (kSegCols * 4), a.x + static_cast<size_t>(t) * a.cols + seg * kSegCols,
-                          static_cast<uint32_t>(cols_here * 4), xfull + xstage);
+                          static_cast<uint32_t>(cols_here * 4), xfull + xstage * 8);
     };
 
     // Weight issue side: lane r (< rows of the chunk) walks the byte range of row `i_row0 + r`, one segment per step.
     int i_chunk = 0, i_row0 = my_begin, i_nrows = chunk_base + (0 < chunk_rem ? 1 : 0), i_seg = 0, i_stage = 0;
+    uintptr_t i_row_at = row_address(a, i_row0 + lane);
     auto issue_w = [&]() {
         if (i_nrows > 0) {  // warp-uniform
             uint32_t bytes = 0;
             uintptr_t src = 0;
             if (lane < i_nrows) {
-                const long long off = static_cast<long long>(i_seg) * SEG;
+                const long long off = static_cast<long long>(seg_begin + i_seg) * SEG;
                 const long long len = a.row_bytes - off < SEG ? a.row_bytes - off : SEG;
-                const uintptr_t p = wbase + static_cast<uintptr_t>(i_row0 + lane) * static_cast<uintptr_t>(a.row_bytes) + off;
+                const uintptr_t p = i_row_at + off;
                 src = p & ~static_cast<uintptr_t>(15);
                 bytes = static_cast<uint32_t>((p - src + len + 15) & ~static_cast<uintptr_t>(15));
             }
             const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
-            if (lane == 0) mbar_expect_tx(bar + i_stage, total);
+            if (lane == 0) mbar_expect_tx(bar + i_stage * 8, total);
             __syncwarp();
-            if (bytes) bulk_copy_g2s(buf + (i_stage * RW + lane) * SLOT, reinterpret_cast<const void *>(src), bytes, bar + i_stage);
+            if (bytes) bulk_copy_g2s(buf + (i_stage * RW + lane) * SLOT, reinterpret_cast<const void *>(src), bytes, bar + i_stage * 8);
             if (++i_stage == S) i_stage = 0;
         }
         if (++i_seg == n_seg) {
@@ -202,6 +239,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
             i_row0 += i_nrows;
             ++i_chunk;
             i_nrows = chunk_base + (i_chunk < chunk_rem ? 1 : 0);
+            i_row_at = row_address(a, i_row0 + lane);
         }
     };
 
@@ -245,7 +283,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
     }
     if (threadIdx.x == 0) {
         const int n = n_steps < XS ? n_steps : XS;
-        for (int s = 0; s < n; ++s) issue_x(s, s % n_seg);
+        for (int s = 0; s < n; ++s) issue_x(s, seg_begin + s % n_seg);
     }
 
     if constexpr (TABLE > 0) {
@@ -271,27 +309,21 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
     int stage = 0, xstage = 0, seg = 0, chunk = 0, row0 = my_begin, nrows = chunk_base + (0 < chunk_rem ? 1 : 0);
     uint32_t phase = 0, xphase = 0;
     for (int step = 0; step < n_steps; ++step) {
-        if (!mbar_wait_bounded(xfull + xstage, xphase)) {
+        if (!mbar_wait_bounded(xfull + xstage * 8, xphase)) {
             expired = true;
             break;
         }
         const bool active = nrows > 0;
         if (active) {
-            if (!mbar_wait_bounded(bar + stage, phase)) {
+            if (!mbar_wait_bounded(bar + stage * 8, phase)) {
                 expired = true;
                 break;
             }
-            const uint8_t *stage_buf = buf + stage * RW * SLOT;
-            // where row 0's segment starts inside its slot (the copy began at the 16-byte boundary below it)
-            const uint32_t d0 = kAligned ? 0u : (static_cast<uint32_t>(wbase & 15u) + static_cast<uint32_t>(row0) * rb16 +
-                                                 static_cast<uint32_t>(seg) * (SEG & 15)) & 15u;
-            const int cols_here = a.cols - seg * kSegCols < kSegCols ? a.cols - seg * kSegCols : kSegCols;
-#ifdef VQM_PROBE_NO_COMPUTE  // experiment: stream the weights through the pipeline without decoding them
-            acc[0][0] += static_cast<unsigned long long>(stage_buf[d0 + lane]);
-#else
-            StepT::run(smem_u32(stage_buf), d0, kAligned ? 0u : rb16, smem_u32(scratch), smem_u32(table), smem_u32(xbuf + xstage * XSTAGE),
-                       cols_here, nrows, acc, lane);
-#endif
+            // d0: where row 0's segment starts inside its slot (the copy began at the 16-byte boundary below it)
+            const int seg_abs = seg_begin + seg;
+            const uint32_t d0 = kAligned ? 0u : (w_align + static_cast<uint32_t>(row0) * rb16 + static_cast<uint32_t>(seg_abs) * (SEG & 15)) & 15u;
+            const int cols_here = a.cols - seg_abs * kSegCols < kSegCols ? a.cols - seg_abs * kSegCols : kSegCols;
+            StepT::run(buf + stage * RW * SLOT, d0, kAligned ? 0u : rb16, scratch, smem0, xbuf + xstage * XSTAGE, cols_here, nrows, acc, lane);
         }
         __syncwarp();
         // Done with the activation stage; the last warp of the block to get here refills it.
@@ -302,7 +334,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                 __threadfence_block();
                 if (step + XS < n_steps) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    issue_x(xstage, (seg + XS) % n_seg);
+                    issue_x(xstage, seg_begin + (seg + XS) % n_seg);
                 }
             }
         }
@@ -325,20 +357,25 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
                         if (lane == r * M + t) mine = s;
                         acc[r][t] = 0ull;
                     }
-                mine *= StepT::kOutScale;  // exact: 1 or a power of two (see bytes_to_subpair)
                 if (lane < RW * M) {
                     const int r = lane / M, t = lane % M, row = row0 + r;
                     if (r < nrows) {
-                        if (a.y != nullptr) a.y[static_cast<size_t>(t) * a.rows + row] = mine;
-                        if (a.push.push_slot > 0) {
-                            // row-sharded: the value also goes straight into every rank's gathered [M][rows_total] vector
-                            const size_t at = static_cast<size_t>(t) * a.push.rows_total + a.push.row_begin + row;
-                            for (int p = 0; p < a.push.n_ranks; ++p)
-                                reinterpret_cast<float *>(a.push.region[p] + a.push.dst_off)[at] = mine;
-                        }
-                        if (want_argmax && better(mine, row, best_v, best_i)) {
-                            best_v = mine;
-                            best_i = row;
+                        if (k_split > 1) {
+                            // this block's share of the columns only; the group's last block adds the shares up
+                            a.split_partial[static_cast<size_t>(kpart * M + t) * a.rows + row] = mine;
+                        } else {
+                            mine *= StepT::kOutScale;  // exact: 1 or a power of two (see bytes_to_subpair)
+                            const RowHome h = home_of(a, row);
+                            if (h.y != nullptr) h.y[static_cast<size_t>(t) * h.rows + h.local] = mine;
+                            if (a.push.push_slot > 0) {
+                                // row-sharded: the value also goes straight into every rank's gathered [M][rows_total] vector
+                                const size_t at = static_cast<size_t>(t) * h.rows_total + h.row_begin + h.local;
+                                for (int p = 0; p < a.push.n_ranks; ++p) reinterpret_cast<float *>(a.push.region[p] + h.dst_off)[at] = mine;
+                            }
+                            if (want_argmax && better(mine, row, best_v, best_i)) {
+                                best_v = mine;
+                                best_i = row;
+                            }
                         }
                     }
                 }
@@ -363,7 +400,35 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M)) qmv_kernel(con
     if (expired) {
         if (lane == 0) atomicExch(a.status, kStatusWaitExpired);
         // give the copies still in flight into this warp's buffers one more bounded chance to land
-        for (int s = 0; s < S; ++s) (void)mbar_wait_bounded(bar + s, 0);
+        for (int s = 0; s < S; ++s) (void)mbar_wait_bounded(bar + s * 8, 0);
+    }
+
+    if (k_split > 1) {
+        // The last block of the group to get here owns the group's outputs: partial sums are added in the order of the
+        // column ranges, whatever order the blocks finished in.
+        __shared__ bool s_reduce;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_reduce = atomicAdd(a.split_counters + group, 1u) == static_cast<unsigned>(k_split - 1);
+        __syncthreads();
+        if (s_reduce) {
+            __threadfence();
+            const int g0 = group * kWarps, g1 = g0 + kWarps;
+            const int row_lo = g0 * base + (g0 < rem ? g0 : rem), row_hi = g1 * base + (g1 < rem ? g1 : rem);
+            for (int i = threadIdx.x; i < (row_hi - row_lo) * M; i += blockDim.x) {
+                const int row = row_lo + i / M, t = i % M;
+                float sum = 0.0f;
+                for (int k = 0; k < k_split; ++k) sum += __ldcg(a.split_partial + static_cast<size_t>(k * M + t) * a.rows + row);
+                sum *= StepT::kOutScale;
+                const RowHome h = home_of(a, row);
+                if (h.y != nullptr) h.y[static_cast<size_t>(t) * h.rows + h.local] = sum;
+                if (a.push.push_slot > 0) {
+                    const size_t at = static_cast<size_t>(t) * h.rows_total + h.row_begin + h.local;
+                    for (int p = 0; p < a.push.n_ranks; ++p) reinterpret_cast<float *>(a.push.region[p] + h.dst_off)[at] = sum;
+                }
+            }
+            if (threadIdx.x == 0) a.split_counters[group] = 0;
+        }
     }
 
     const bool want_push = a.push.push_slot > 0;

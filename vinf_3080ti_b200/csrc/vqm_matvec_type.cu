@@ -52,6 +52,7 @@ struct Variant {
     static cudaError_t launch(const MatvecArgs &a, int sm_count, cudaStream_t stream, int *grid_out) {
         if constexpr (kFits) {
             int grid = grid_for(a.rows, sm_count, blocks_per_sm());
+            if (a.k_split > 1) grid = (a.rows + kWarps - 1) / kWarps * a.k_split;  // one row per warp, k_split blocks per group
             if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
             if (grid_out != nullptr) *grid_out = grid;
             cudaLaunchConfig_t cfg{};
@@ -71,8 +72,27 @@ struct Variant {
     }
 };
 
+// Column split for short launches.  When the rows cover less than half of the warps a full grid has (two blocks per SM
+// of kWarps warps - a nominal figure, so that the choice never depends on M and an M-row pass stays equal to M
+// single-row passes bit for bit), every row goes to one warp of a group and k blocks per group share the column
+// segments: k = warps / rows, at most kMaxSplit and at most one block per segment.
+inline int choose_split(const MatvecArgs &a, int sm_count) {
+    if (a.split_partial == nullptr || a.out_idx != nullptr) return 1;
+    const int warps = sm_count * 2 * kWarps, n_seg = (a.cols + kSegCols - 1) / kSegCols;
+    if (a.rows * 2 > warps) return 1;
+    int k = warps / a.rows;
+    if (k > kMaxSplit) k = kMaxSplit;
+    if (k > n_seg) k = n_seg;
+    if ((a.rows + kWarps - 1) / kWarps > kSplitGroups) return 1;
+    if (static_cast<long long>(k) * kMaxTok * a.rows > a.split_capacity) return 1;
+    return k;
+}
+
 template <int M>
-cudaError_t launch_one(const MatvecArgs &a, int sm_count, cudaStream_t stream, int *grid_out) {
+cudaError_t launch_one(const MatvecArgs &args, int sm_count, cudaStream_t stream, int *grid_out) {
+    MatvecArgs a = args;
+    a.k_split = choose_split(a, sm_count);
+    if (a.k_split > 1) return Variant<M, 1>::launch(a, sm_count, stream, grid_out);
     constexpr int kMaxRw = 4;  // taller chunks cost a block per SM (shared memory) and more than they save
     // smallest RW that holds a warp's share; the tallest that can run if the share needs several chunks anyway
     if (const int n = Variant<M, 1>::rows_per_warp(a.rows, sm_count); n > 0 && n <= 1) return Variant<M, 1>::launch(a, sm_count, stream, grid_out);

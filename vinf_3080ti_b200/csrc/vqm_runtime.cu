@@ -5,6 +5,7 @@
 // :2167-2197 argmax, :2281-2315 matvec).  Weights are always resident: there is no host ring or VMM group.
 #include <cuda_runtime.h>
 
+#include <climits>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -77,6 +78,8 @@ struct vqm_runtime {
     int *part_idx = nullptr;
     int *argmax_ids = nullptr;     // [256]: fused argmax uses the first 8, argmax_rows up to 256
     float *argmax_vals = nullptr;  // [8]
+    float *split_partial = nullptr;      // column-split launches: partial sums [k][M][rows]
+    unsigned *split_counters = nullptr;  // ... and one arrival counter per row group
     // scratch of the synchronous matvec entry
     float *scratch_x = nullptr, *scratch_y = nullptr;
     size_t scratch_x_n = 0, scratch_y_n = 0;
@@ -173,23 +176,46 @@ int check_shape(const char *name, int type, int cols, int rows, size_t *row_byte
     return VQM_OK;
 }
 
-// Launches y = W x for m <= 8 rows of x, optionally with the fused argmax.
-int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int m, bool with_argmax,
+constexpr int kSplitPartialFloats = vqm::kMaxSplit * 8 * 2048;  // k ranges x 8 activation rows x rows of a short launch
+
+void set_single_part(vqm::MatvecArgs &a, const uint8_t *w, float *y, int rows) {
+    for (int i = 0; i < vqm::kMaxParts; ++i) a.part[i] = vqm::MatvecPart{nullptr, nullptr, INT_MAX, 0};
+    a.part[0] = vqm::MatvecPart{w, y, rows, rows};
+    a.rows = rows;
+    a.k_split = 1;
+}
+
+// Launches y_p = W_p x for the n tensors of a group (same type and columns; one launch) and m <= 8 rows of x,
+// optionally with the fused argmax (n = 1 only).
+int launch_parts(vqm_runtime *rt, int n, const Tensor *const *ts, const float *x, float *const *ys, int m, bool with_argmax,
                  const vqm::PushInfo *push = nullptr) {
-    const uint8_t *cb = codebook_for(rt, t.type);
-    if (vqm::grid_is_codebook(t.type) && cb == nullptr)
-        return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t.type);
+    const Tensor &t0 = *ts[0];
+    const uint8_t *cb = codebook_for(rt, t0.type);
+    if (vqm::grid_is_codebook(t0.type) && cb == nullptr)
+        return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t0.type);
     vqm::MatvecArgs a{};
-    a.w = t.data;
+    set_single_part(a, t0.data, ys[0], t0.rows);
+    long long rows = t0.rows;
+    for (int i = 1; i < n; ++i) {
+        // the kernel derives where a row's bytes start inside its 16-byte line from the launch row number
+        const uintptr_t want = (reinterpret_cast<uintptr_t>(t0.data) + static_cast<uintptr_t>(rows) * t0.row_bytes) & 15u;
+        if ((reinterpret_cast<uintptr_t>(ts[i]->data) & 15u) != want)
+            return fail(VQM_ERR_VALUE, "tensor %d of the group cannot follow the others in one launch (row alignment); launch it alone", i);
+        rows += ts[i]->rows;
+        if (rows > INT_MAX) return fail(VQM_ERR_VALUE, "too many rows in one launch");
+        a.part[i] = vqm::MatvecPart{ts[i]->data, ys[i], static_cast<int>(rows), ts[i]->rows};
+    }
+    a.rows = static_cast<int>(rows);
     a.x = x;
-    a.y = y;
     a.codebook = cb;
     a.status = rt->status;
-    a.rows = t.rows;
-    a.cols = t.cols;
-    a.row_bytes = static_cast<long long>(t.row_bytes);
+    a.cols = t0.cols;
+    a.row_bytes = static_cast<long long>(t0.row_bytes);
     a.overlap_launch = rt->overlap_launch;
     a.max_grid = vqm::kMaxGrid;
+    a.split_partial = rt->split_partial;
+    a.split_counters = rt->split_counters;
+    a.split_capacity = kSplitPartialFloats;
     if (push != nullptr) {
         a.push = *push;
         a.done_counter = rt->done_counter;
@@ -200,11 +226,35 @@ int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int
         a.done_counter = rt->done_counter;
         a.out_idx = rt->argmax_ids;
         a.out_val = rt->argmax_vals;
-        a.row_base = t.argmax_row_base;
+        a.row_base = t0.argmax_row_base;
     }
-    const cudaError_t err = dispatch_qmv(t.type, a, m, rt->sm_count, rt->stream, nullptr);
+    const cudaError_t err = dispatch_qmv(t0.type, a, m, rt->sm_count, rt->stream, nullptr);
     if (err != cudaSuccess) return cuda_fail("qmv launch", err);
     count_launch(rt);
+    return VQM_OK;
+}
+
+int launch_group(vqm_runtime *rt, const Tensor &t, const float *x, float *y, int m, bool with_argmax, const vqm::PushInfo *push = nullptr) {
+    const Tensor *ts[1] = {&t};
+    float *ys[1] = {y};
+    return launch_parts(rt, 1, ts, x, ys, m, with_argmax, push);
+}
+
+// The tensors and output buffers of a group call, checked: same type and columns, every y large enough.
+int resolve_group(vqm_runtime *rt, int n, const char *const *weights, const char *const *ys, int ntok, const Tensor **ts, float **yps) {
+    if (n < 1 || n > vqm::kMaxParts) return fail(VQM_ERR_VALUE, "a group holds 1 to %d tensors", vqm::kMaxParts);
+    if (weights == nullptr || ys == nullptr) return fail(VQM_ERR_VALUE, "null pointer");
+    int rc = VQM_OK;
+    for (int i = 0; i < n; ++i) {
+        const Tensor *t = find_tensor(rt, weights[i], &rc);
+        if (t == nullptr) return rc;
+        if (t->cols % 32 != 0) return fail(VQM_ERR_VALUE, "%s: matvec cols must be a multiple of 32", weights[i]);
+        if (i > 0 && (t->type != ts[0]->type || t->cols != ts[0]->cols))
+            return fail(VQM_ERR_VALUE, "%s: the tensors of a group must share their GGUF type and their columns", weights[i]);
+        ts[i] = t;
+        yps[i] = find_f32(rt, ys[i], static_cast<size_t>(t->rows) * ntok, &rc);
+        if (yps[i] == nullptr) return rc;
+    }
     return VQM_OK;
 }
 
@@ -243,6 +293,9 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
     if (err == cudaSuccess) err = cudaMalloc(&rt->part_idx, sizeof(int) * 8 * vqm::kMaxGrid);
     if (err == cudaSuccess) err = cudaMalloc(&rt->argmax_ids, sizeof(int) * 256);
     if (err == cudaSuccess) err = cudaMalloc(&rt->argmax_vals, sizeof(float) * 8);
+    if (err == cudaSuccess) err = cudaMalloc(&rt->split_partial, sizeof(float) * kSplitPartialFloats);
+    if (err == cudaSuccess) err = cudaMalloc(&rt->split_counters, sizeof(unsigned) * vqm::kSplitGroups);
+    if (err == cudaSuccess) err = cudaMemset(rt->split_counters, 0, sizeof(unsigned) * vqm::kSplitGroups);
     if (err != cudaSuccess) {
         const int rc = cuda_fail("runtime setup", err);
         vqm_runtime_destroy(rt);
@@ -250,6 +303,10 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
     }
     rt->done_counter = rt->status + 16;
     if (const char *e = getenv("VINF_B200_NO_PDL"); e != nullptr && e[0] == '1') rt->overlap_launch = 0;
+    if (const char *e = getenv("VINF_B200_NO_SPLIT"); e != nullptr && e[0] == '1') {  // never split short launches by columns
+        cudaFree(rt->split_partial);
+        rt->split_partial = nullptr;
+    }
     if (iq3s_grid != nullptr) {
         const int rc = vqm_set_codebook(rt, "iq3s_grid", iq3s_grid, nbytes);
         if (rc != VQM_OK) {
@@ -275,6 +332,8 @@ void vqm_runtime_destroy(vqm_runtime *rt) {
     cudaFree(rt->part_idx);
     cudaFree(rt->argmax_ids);
     cudaFree(rt->argmax_vals);
+    cudaFree(rt->split_partial);
+    cudaFree(rt->split_counters);
     cudaFree(rt->scratch_x);
     cudaFree(rt->scratch_y);
     cudaFree(rt->gemm_x);
@@ -556,8 +615,6 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
             if ((rc = no_capture(rt, "growing the prompt-pass activation buffer")) != VQM_OK) return rc;
             cudaStreamSynchronize(rt->stream);
             cudaFree(rt->gemm_x);
-    for (void *p : rt->exchange_opened) cudaIpcCloseMemHandle(p);
-    cudaFree(rt->exchange_own);
             rt->gemm_x = nullptr;
             rt->gemm_x_len = 0;
             err = cudaMalloc(&rt->gemm_x, need * 2);
@@ -858,13 +915,52 @@ int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char 
     float *yp = find_f32(rt, y, static_cast<size_t>(t->rows) * ntok, &rc);
     if (yp == nullptr) return rc;
     vqm::PushInfo p = rt->push;
-    p.dst_off = static_cast<long long>(dst_off);
-    p.rows_total = rows_total;
-    p.row_begin = row_begin;
+    p.dst_off[0] = static_cast<long long>(dst_off);
+    p.rows_total[0] = rows_total;
+    p.row_begin[0] = row_begin;
     p.push_slot = slot + 1;
     p.wait_slot = wait_slot + 1;
     p.wait_lag = wait_lag;
     return launch_group(rt, *t, xp, yp, ntok, with_argmax != 0, &p);
+}
+
+int vqm_qmv_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok) {
+    if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8]");
+    const Tensor *ts[vqm::kMaxParts];
+    float *yps[vqm::kMaxParts];
+    int rc = resolve_group(rt, n, weights, ys, ntok, ts, yps);
+    if (rc != VQM_OK) return rc;
+    const float *xp = find_f32(rt, x, static_cast<size_t>(ts[0]->cols) * ntok, &rc);
+    if (xp == nullptr) return rc;
+    return launch_parts(rt, n, ts, xp, yps, ntok, false);
+}
+
+int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok, int slot,
+                       const size_t *dst_offs, const int *rows_totals, const int *row_begins, int wait_slot, int wait_lag) {
+    if (rt->push.n_ranks == 0) return fail(VQM_ERR_VALUE, "exchange_config has not been called");
+    if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8]");
+    if (slot < -1 || slot >= rt->exchange_slots || wait_slot < -1 || wait_slot >= rt->exchange_slots || wait_lag < 0 || wait_lag > 1)
+        return fail(VQM_ERR_VALUE, "slot out of range");
+    if (dst_offs == nullptr || rows_totals == nullptr || row_begins == nullptr) return fail(VQM_ERR_VALUE, "null pointer");
+    const Tensor *ts[vqm::kMaxParts];
+    float *yps[vqm::kMaxParts];
+    int rc = resolve_group(rt, n, weights, ys, ntok, ts, yps);
+    if (rc != VQM_OK) return rc;
+    const float *xp = find_f32(rt, x, static_cast<size_t>(ts[0]->cols) * ntok, &rc);
+    if (xp == nullptr) return rc;
+    vqm::PushInfo p = rt->push;
+    for (int i = 0; i < n; ++i) {
+        if (rows_totals[i] < ts[i]->rows || row_begins[i] < 0 || row_begins[i] + ts[i]->rows > rows_totals[i] || (dst_offs[i] & 15u) != 0)
+            return fail(VQM_ERR_VALUE, "%s: slice [%d, %d) does not fit %d rows, or dst_off is not 16-byte aligned", weights[i], row_begins[i],
+                        row_begins[i] + ts[i]->rows, rows_totals[i]);
+        p.dst_off[i] = static_cast<long long>(dst_offs[i]);
+        p.rows_total[i] = rows_totals[i];
+        p.row_begin[i] = row_begins[i];
+    }
+    p.push_slot = slot + 1;
+    p.wait_slot = wait_slot + 1;
+    p.wait_lag = wait_lag;
+    return launch_parts(rt, n, ts, xp, yps, ntok, false, &p);
 }
 
 int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
@@ -886,12 +982,10 @@ int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, flo
         if (err != cudaSuccess) return cuda_fail("device query", err);
     }
     vqm::MatvecArgs a{};
-    a.w = static_cast<const uint8_t *>(w);
+    set_single_part(a, static_cast<const uint8_t *>(w), y, rows);
     a.x = x;
-    a.y = y;
     a.codebook = static_cast<const uint8_t *>(codebook);
     a.status = status;
-    a.rows = rows;
     a.cols = cols;
     a.row_bytes = static_cast<long long>(row_bytes);
     const cudaError_t err = dispatch_qmv(type, a, ntok, sm_count, static_cast<cudaStream_t>(stream), nullptr);
@@ -950,9 +1044,8 @@ int vqm_qmv_argmax_static(int type, const void *w, int rows, int cols, const flo
     err = cudaMemsetAsync(&scratch->done_counter, 0, sizeof(unsigned), st);
     if (err != cudaSuccess) return cuda_fail("scratch reset", err);
     vqm::MatvecArgs a{};
-    a.w = static_cast<const uint8_t *>(w);
+    set_single_part(a, static_cast<const uint8_t *>(w), y, rows);
     a.x = x;
-    a.y = y;
     a.codebook = static_cast<const uint8_t *>(codebook);
     a.status = status;
     a.part_val = scratch->part_val;
@@ -960,7 +1053,6 @@ int vqm_qmv_argmax_static(int type, const void *w, int rows, int cols, const flo
     a.done_counter = &scratch->done_counter;
     a.out_idx = out_ids;
     a.out_val = out_values;
-    a.rows = rows;
     a.cols = cols;
     a.row_bytes = static_cast<long long>(row_bytes);
     a.max_grid = kStaticMaxBlocks;  // the launch never uses more blocks than the scratch has partial slots for

@@ -302,6 +302,29 @@ class Runtime:
         _capi.check(self._lib.vqm_qmv_push(self._h, _name(weight), _name(x), _name(y), int(ntok), int(slot), int(dst_off), int(rows_total),
                                            int(row_begin), int(wait_slot), int(wait_lag), int(with_argmax)))
 
+    def qmv_group(self, weights: list[str], x: str, ys: list[str], ntok: int) -> None:
+        """ys[i] = W_i x for up to four tensors that share x, their GGUF type and their columns, in ONE launch
+        (q/k/v of an attention layer, gate/up of an FFN).  No counterpart in the reference, which launches one
+        kernel per tensor (engine/csrc/megakernel/qwen_runtime.cu:1259-1296)."""
+        if len(weights) != len(ys):
+            raise ValueError("one output buffer per tensor")
+        n = len(weights)
+        w = (ctypes.c_char_p * n)(*[_name(v) for v in weights])
+        y = (ctypes.c_char_p * n)(*[_name(v) for v in ys])
+        _capi.check(self._lib.vqm_qmv_group(self._h, n, w, _name(x), y, int(ntok)))
+
+    def qmv_push_group(self, weights: list[str], x: str, ys: list[str], ntok: int, slot: int, dst_offs: list[int],
+                       rows_totals: list[int], row_begins: list[int], wait_slot: int = -1, wait_lag: int = 0) -> None:
+        """qmv_group on this rank's row slices fused with their all-gathers: one flag slot for the launch."""
+        n = len(weights)
+        if not (len(ys) == len(dst_offs) == len(rows_totals) == len(row_begins) == n):
+            raise ValueError("one entry per tensor")
+        w = (ctypes.c_char_p * n)(*[_name(v) for v in weights])
+        y = (ctypes.c_char_p * n)(*[_name(v) for v in ys])
+        _capi.check(self._lib.vqm_qmv_push_group(self._h, n, w, _name(x), y, int(ntok), int(slot), (ctypes.c_size_t * n)(*dst_offs),
+                                                 (ctypes.c_int * n)(*rows_totals), (ctypes.c_int * n)(*row_begins), int(wait_slot),
+                                                 int(wait_lag)))
+
     # ---- residency machinery of the reference: everything is resident here ------------------------------
     # (engine/csrc/megakernel/qwen_runtime.cu:1485-1811; engine/src/vinf/gguf/residency.py:256-354)
     def vram_bytes(self) -> int:
