@@ -38,21 +38,33 @@ constexpr int kWarps = 8;                      // warps per block
 constexpr int kMaxTok = 8;                     // activation rows per launch
 constexpr int kWarpSmemBudget = 5120;          // weight staging bytes a warp aims for (at least two stages are kept)
 constexpr int kBarrierBytes = 1024;            // mbarriers and counters at the front of shared memory
-constexpr int kXStageBudget = 49152;           // activation staging bytes a block aims for (at least two stages)
 
 __host__ __device__ constexpr int stages_for(int type, int rw) {
     const int s = kWarpSmemBudget / (rw * slot_bytes(type));
     return s < 2 ? 2 : s > 8 ? 8 : s;
 }
-__host__ __device__ constexpr int x_stages_for(int m) {
-    const int s = kXStageBudget / (m * kSegCols * 4);
+__host__ __device__ constexpr int table_bytes_padded(int type) { return (grid_bytes(type) + 15) / 16 * 16; }
+
+// Blocks per SM the register allocation aims for: two, except for the tall chunks of wide passes (their sums alone
+// take RW * M register pairs).  One-row chunks always get two, which the column split of short launches counts on.
+#ifndef VQM_MIN_BLOCKS
+#define VQM_MIN_BLOCKS(M, RW) (((M) <= 4 || (RW) == 1) ? 2 : 1)
+#endif
+
+// Activation stages: as many (2..4) as leave room for the blocks per SM the kernel aims for (228 KB of shared memory per
+// SM, 1 KB of it reserved per block).
+template <int TYPE, int M, int RW>
+__host__ __device__ constexpr int x_stages() {
+    constexpr int fixed = table_bytes_padded(TYPE) + kBarrierBytes + kWarps * stages_for(TYPE, RW) * RW * slot_bytes(TYPE) +
+                          kWarps * Step<TYPE, M, RW>::kScratch;
+    constexpr int budget = (VQM_MIN_BLOCKS(M, RW) >= 2 ? 112 : 200) * 1024;
+    constexpr int s = (budget - fixed) / (M * kSegCols * 4);
     return s < 2 ? 2 : s > 4 ? 4 : s;
 }
-__host__ __device__ constexpr int table_bytes_padded(int type) { return (grid_bytes(type) + 15) / 16 * 16; }
-__host__ __device__ constexpr size_t matvec_smem_bytes(int type, int rw, int m) {
-    return static_cast<size_t>(table_bytes_padded(type)) + kBarrierBytes +
-           static_cast<size_t>(x_stages_for(m)) * m * kSegCols * 4 +
-           static_cast<size_t>(kWarps) * stages_for(type, rw) * rw * slot_bytes(type);
+template <int TYPE, int RW, int M>
+__host__ __device__ constexpr size_t matvec_smem_bytes_for() {
+    return static_cast<size_t>(table_bytes_padded(TYPE)) + kBarrierBytes + static_cast<size_t>(x_stages<TYPE, M, RW>()) * M * kSegCols * 4 +
+           static_cast<size_t>(kWarps) * stages_for(TYPE, RW) * RW * slot_bytes(TYPE) + static_cast<size_t>(kWarps) * Step<TYPE, M, RW>::kScratch;
 }
 
 // ---- mbarrier / bulk-copy primitives ---------------------------------------------------------------
@@ -137,21 +149,11 @@ __device__ __forceinline__ uintptr_t row_address(const MatvecArgs &a, int g) {
 
 // ---- the kernel ------------------------------------------------------------------------------------------
 
-template <int TYPE, int RW, int M>
-__host__ __device__ constexpr size_t matvec_smem_bytes_for() {
-    return matvec_smem_bytes(TYPE, RW, M) + static_cast<size_t>(kWarps) * Step<TYPE, M, RW>::kScratch;
-}
-
-// Blocks per SM the register allocation aims for: two, except for the tall chunks of wide passes (their sums alone
-// take RW * M register pairs).  One-row chunks always get two, which the column split of short launches counts on.
-#ifndef VQM_MIN_BLOCKS
-#define VQM_MIN_BLOCKS(M, RW) (((M) <= 4 || (RW) == 1) ? 2 : 1)
-#endif
 template <int TYPE, int M, int RW>
 __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel(const MatvecArgs a) {
     using StepT = Step<TYPE, M, RW>;
     constexpr int S = stages_for(TYPE, RW);
-    constexpr int XS = x_stages_for(M);
+    constexpr int XS = x_stages<TYPE, M, RW>();
     constexpr int SLOT = slot_bytes(TYPE);
     constexpr int SEG = seg_bytes(TYPE);
     constexpr int TABLE = table_bytes_padded(TYPE);
