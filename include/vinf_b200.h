@@ -186,14 +186,18 @@ int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char 
  * launch treats their rows as one list, so short tensors ride along with long ones instead of paying for a launch
  * each.  Every output equals, bit for bit, what vqm_qmv gives for its tensor alone, unless one of the two launches
  * is short enough to be split by columns (a launch whose rows would leave more than half of the GPU's warps idle
- * shares each row's columns among up to 8 blocks and adds their partial sums in column order; the grouping of the
- * additions then depends on the number of rows in the launch, never on ntok).
+ * shares each row's columns among the up to 8 blocks of a thread-block cluster and adds their partial sums in column
+ * order; the grouping of the additions then depends on the number of rows in the launch, never on ntok).
  *   n: 1..4 tensors; ntok: 1..8.  VQM_ERR_VALUE if the tensors do not share type and columns, or if a tensor's rows
  *   cannot follow the previous tensor's in one launch (for types whose rows are not multiples of 16 bytes, the row
  *   counts of all but the last tensor have to keep the rows' position within a 16-byte line going).
  * vqm_qmv_push_group is the row-sharded form (see vqm_qmv_push): per tensor its place in the gathered vectors, one
  * flag slot for the whole launch. */
 int vqm_qmv_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok);
+/* Column split of short launches on (default) or off.  Off: every output is one warp's sum over all columns, so a
+ * tensor's outputs do not depend on what else is in its launch; on: see above.  (The environment variable
+ * VINF_B200_NO_SPLIT=1 sets the default to off.) */
+int vqm_set_column_split(vqm_runtime *rt, int enabled);
 int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok, int slot,
                        const size_t *dst_offs, const int *rows_totals, const int *row_begins, int wait_slot, int wait_lag);
 

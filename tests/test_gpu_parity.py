@@ -399,7 +399,7 @@ def _upload_group(rt, t, shapes, cols, ntok, rng):
                                             (T.IQ4_XS, (1400, 3), 3), (T.IQ3_S, (1500, 700), 2)], ids=lambda v: getattr(v, "name", str(v)))
 def test_group_launch_equals_one_launch_per_tensor_bit_for_bit(rt, codebooks, t, shapes, ntok):
     """q/k/v-like and gate/up-like groups: one launch over all rows gives every tensor exactly what its own launch
-    gives (1024 columns: a single column segment, so neither launch can be split by columns)."""
+    gives, as long as short launches are not split by columns (the short tensors' own launches would be)."""
     rng = np.random.default_rng(sum(shapes) + ntok)
     cols = 1024
     raws = _upload_group(rt, t, shapes, cols, ntok, rng)
@@ -407,10 +407,14 @@ def test_group_launch_equals_one_launch_per_tensor_bit_for_bit(rt, codebooks, t,
     rt.alloc("x", ntok * cols)
     rt.write("x", x)
     n = len(shapes)
-    rt.qmv_group([f"g{i}" for i in range(n)], "x", [f"gy{i}" for i in range(n)], ntok)
-    for i in range(n):
-        rt.qmv(f"g{i}", "x", f"sy{i}", ntok)
-    rt.synchronize()
+    rt.set_column_split(False)
+    try:
+        rt.qmv_group([f"g{i}" for i in range(n)], "x", [f"gy{i}" for i in range(n)], ntok)
+        for i in range(n):
+            rt.qmv(f"g{i}", "x", f"sy{i}", ntok)
+        rt.synchronize()
+    finally:
+        rt.set_column_split(True)
     for i, rows in enumerate(shapes):
         grouped = rt.read_array(f"gy{i}", ntok * rows)
         assert np.array_equal(grouped.view(np.uint32), rt.read_array(f"sy{i}", ntok * rows).view(np.uint32)), i

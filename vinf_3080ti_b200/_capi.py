@@ -73,6 +73,7 @@ SIGNATURES: dict[str, list] = {
     "vqm_exchange_config": [c_void_p, c_int, c_int, POINTER(c_uint64), c_size_t, c_size_t, c_int],
     "vqm_exchange_next_pass": [c_void_p],
     "vqm_qmv_push": [c_void_p, c_char_p, c_char_p, c_char_p, c_int, c_int, c_size_t, c_int, c_int, c_int, c_int, c_int],
+    "vqm_set_column_split": [c_void_p, c_int],
     "vqm_qmv_group": [c_void_p, c_int, POINTER(c_char_p), c_char_p, POINTER(c_char_p), c_int],
     "vqm_qmv_push_group": [c_void_p, c_int, POINTER(c_char_p), c_char_p, POINTER(c_char_p), c_int, c_int, POINTER(c_size_t),
                            POINTER(c_int), POINTER(c_int), c_int, c_int],

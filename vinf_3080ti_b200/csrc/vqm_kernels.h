@@ -47,20 +47,17 @@ struct MatvecArgs {
     int rows, cols;          // rows: of all tensors together
     long long row_bytes;
     int row_base;            // added to row numbers reported by the argmax (row-sharded weights)
-    // Column split for short launches: k_split blocks share a group of rows, each takes a range of the column segments
-    // and leaves partial sums in split_partial[k][M][rows]; the last of them to finish adds the partials in the order
-    // of k and writes the outputs.  split_counters: one per row group, zero between launches.
+    // Column split for short launches: the k_split blocks of a thread-block cluster share a group of rows (one row per
+    // warp), each takes a range of the column segments and leaves its partial sums in the shared memory of the
+    // cluster's first block, which adds them in the order of k and writes the outputs.
     int k_split;             // chosen by the launcher (from the rows and the columns only, never from M); 1 = off
-    float *split_partial;    // null: never split
-    unsigned *split_counters;
-    int split_capacity;      // floats in split_partial
+    int allow_split;         // host only: the caller permits the split
     int overlap_launch;      // host only: launch with programmatic stream serialization (see qmv_kernel)
     int max_grid;            // host only: upper bound on the grid (0 = none); sizes the argmax partial arrays
     PushInfo push;           // all zero when the tensor is not sharded
 };
 
-constexpr int kMaxSplit = 8;          // column ranges a row can be split into
-constexpr int kSplitGroups = 4096;    // row groups a split launch can have (size of split_counters)
+constexpr int kMaxSplit = 8;  // column ranges a row can be split into (the portable cluster size)
 
 enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1, kStatusPeerWaitExpired = 2 };
 

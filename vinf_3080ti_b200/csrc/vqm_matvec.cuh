@@ -57,7 +57,7 @@ template <int TYPE, int M, int RW>
 __host__ __device__ constexpr int x_stages() {
     constexpr int fixed = table_bytes_padded(TYPE) + kBarrierBytes + kWarps * stages_for(TYPE, RW) * RW * slot_bytes(TYPE) +
                           kWarps * Step<TYPE, M, RW>::kScratch;
-    constexpr int budget = (VQM_MIN_BLOCKS(M, RW) >= 2 ? 112 : 200) * 1024;
+    constexpr int budget = (VQM_MIN_BLOCKS(M, RW) >= 2 ? 108 : 200) * 1024;  // dynamic part; the kernel has ~5 KB of static arrays
     constexpr int s = (budget - fixed) / (M * kSegCols * 4);
     return s < 2 ? 2 : s > 4 ? 4 : s;
 }
@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     static_assert(RW * M <= 32, "one lane per (row, activation row) output");
     static_assert(kWarps * 8 * 8 + 8 * 8 + 8 * 4 <= kBarrierBytes, "barrier area");
 
+    __shared__ float s_split[kMaxSplit][kWarps][kMaxTok];  // column split: partial sums of the cluster's blocks (first block's copy)
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: lookup table | barriers: [kWarps][8] weight stages, [8] activation stages, [XS] "warps done" counters |
     //         XS activation stages | per warp S x RW weight slots | per warp decoder scratch
@@ -192,27 +193,35 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
 
     // Even split of the rows over the warps: warp gw gets `my_count` consecutive rows from `my_begin`, taken in
     // `n_chunks` chunks of at most RW rows (chunk sizes differ by at most one).  n_chunks is the same for every warp,
-    // so the warps of a block share the activation stages.  With a column split, k_split consecutive blocks form a
-    // group that shares its rows and block `kpart` of the group takes column segments [seg_begin, seg_begin + n_seg).
+    // so the warps of a block share the activation stages.  With a column split, the k_split blocks of a thread-block
+    // cluster form a group that shares its rows (one per warp) and block `kpart` of the cluster takes its share of the
+    // columns.
     const int k_split = a.k_split, n_groups = gridDim.x / k_split, group = blockIdx.x / k_split, kpart = blockIdx.x % k_split;
     const int total_warps = n_groups * kWarps, gw = group * kWarps + warp;
     const int base = a.rows / total_warps, rem = a.rows % total_warps;
     const int my_count = base + (gw < rem ? 1 : 0), my_begin = gw * base + (gw < rem ? gw : rem);
     const int n_chunks = (base + (rem > 0 ? 1 : 0) + RW - 1) / RW;
     const int chunk_base = my_count / n_chunks, chunk_rem = my_count % n_chunks;  // chunk c has chunk_base + (c < chunk_rem) rows
-    const int n_seg_all = (a.cols + kSegCols - 1) / kSegCols;
-    const int seg_begin = kpart * n_seg_all / k_split, n_seg = (kpart + 1) * n_seg_all / k_split - seg_begin;
+    // columns [col_begin, col_end) in n_seg segments of kSegCols (the last one may be shorter); the split is even in
+    // units of 256 columns
+    const int n_units = (a.cols + 255) / 256;
+    const int col_begin = kpart * n_units / k_split * 256;
+    const int col_end = (kpart + 1) * n_units / k_split * 256 < a.cols ? (kpart + 1) * n_units / k_split * 256 : a.cols;
+    const int n_seg = (col_end - col_begin + kSegCols - 1) / kSegCols;
     const int n_steps = n_chunks * n_seg;
+    constexpr int CB = chunk_block(TYPE), CBB = chunk_block_bytes(TYPE);
+    const uint32_t byte_begin = static_cast<uint32_t>(col_begin / CB * CBB), byte_end = static_cast<uint32_t>(col_end / CB * CBB);
     const uint32_t w_align = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(a.part[0].w) & 15u);
     const uint32_t rb16 = static_cast<uint32_t>(a.row_bytes) & 15u;
 
     // Activation stage for step `step` (segment `seg`): one bulk copy per activation row.  Called by one thread.
     auto issue_x = [&](int xstage, int seg) {
-        const int cols_here = a.cols - seg * kSegCols < kSegCols ? a.cols - seg * kSegCols : kSegCols;
+        const int col0 = col_begin + seg * kSegCols;
+        const int cols_here = col_end - col0 < kSegCols ? col_end - col0 : kSegCols;
         mbar_expect_tx(xfull + xstage * 8, static_cast<uint32_t>(M * cols_here * 4));
 #pragma unroll
         for (int t = 0; t < M; ++t)
-            bulk_copy_g2s(xbuf + xstage * XSTAGE + t * (kSegCols * 4), a.x + static_cast<size_t>(t) * a.cols + seg * kSegCols,
+            bulk_copy_g2s(xbuf + xstage * XSTAGE + t * (kSegCols * 4), a.x + static_cast<size_t>(t) * a.cols + col0,
                           static_cast<uint32_t>(cols_here * 4), xfull + xstage * 8);
     };
 
@@ -224,8 +233,8 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
             uint32_t bytes = 0;
             uintptr_t src = 0;
             if (lane < i_nrows) {
-                const long long off = static_cast<long long>(seg_begin + i_seg) * SEG;
-                const long long len = a.row_bytes - off < SEG ? a.row_bytes - off : SEG;
+                const uint32_t off = byte_begin + static_cast<uint32_t>(i_seg) * SEG;
+                const uint32_t len = byte_end - off < SEG ? byte_end - off : SEG;
                 const uintptr_t p = i_row_at + off;
                 src = p & ~static_cast<uintptr_t>(15);
                 bytes = static_cast<uint32_t>((p - src + len + 15) & ~static_cast<uintptr_t>(15));
@@ -285,7 +294,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     }
     if (threadIdx.x == 0) {
         const int n = n_steps < XS ? n_steps : XS;
-        for (int s = 0; s < n; ++s) issue_x(s, seg_begin + s % n_seg);
+        for (int s = 0; s < n; ++s) issue_x(s, s % n_seg);
     }
 
     if constexpr (TABLE > 0) {
@@ -322,9 +331,9 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                 break;
             }
             // d0: where row 0's segment starts inside its slot (the copy began at the 16-byte boundary below it)
-            const int seg_abs = seg_begin + seg;
-            const uint32_t d0 = kAligned ? 0u : (w_align + static_cast<uint32_t>(row0) * rb16 + static_cast<uint32_t>(seg_abs) * (SEG & 15)) & 15u;
-            const int cols_here = a.cols - seg_abs * kSegCols < kSegCols ? a.cols - seg_abs * kSegCols : kSegCols;
+            const uint32_t d0 = kAligned ? 0u : (w_align + static_cast<uint32_t>(row0) * rb16 + byte_begin + static_cast<uint32_t>(seg) * SEG) & 15u;
+            const int col0 = col_begin + seg * kSegCols;
+            const int cols_here = col_end - col0 < kSegCols ? col_end - col0 : kSegCols;
             StepT::run(buf + stage * RW * SLOT, d0, kAligned ? 0u : rb16, scratch, smem0, xbuf + xstage * XSTAGE, cols_here, nrows, acc, lane);
         }
         __syncwarp();
@@ -336,7 +345,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                 __threadfence_block();
                 if (step + XS < n_steps) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    issue_x(xstage, seg_begin + (seg + XS) % n_seg);
+                    issue_x(xstage, (seg + XS) % n_seg);
                 }
             }
         }
@@ -363,8 +372,11 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                     const int r = lane / M, t = lane % M, row = row0 + r;
                     if (r < nrows) {
                         if (k_split > 1) {
-                            // this block's share of the columns only; the group's last block adds the shares up
-                            a.split_partial[static_cast<size_t>(kpart * M + t) * a.rows + row] = mine;
+                            // this block's share of the columns only: it goes into the shared memory of the cluster's first
+                            // block, which adds the shares up (one-row chunks: r = 0, lane = t)
+                            uint32_t remote;
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&s_split[kpart][warp][t])), "r"(0));
+                            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(mine) : "memory");
                         } else {
                             mine *= StepT::kOutScale;  // exact: 1 or a power of two (see bytes_to_subpair)
                             const RowHome h = home_of(a, row);
@@ -406,21 +418,16 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     }
 
     if (k_split > 1) {
-        // The last block of the group to get here owns the group's outputs: partial sums are added in the order of the
-        // column ranges, whatever order the blocks finished in.
-        __shared__ bool s_reduce;
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) s_reduce = atomicAdd(a.split_counters + group, 1u) == static_cast<unsigned>(k_split - 1);
-        __syncthreads();
-        if (s_reduce) {
-            __threadfence();
-            const int g0 = group * kWarps, g1 = g0 + kWarps;
-            const int row_lo = g0 * base + (g0 < rem ? g0 : rem), row_hi = g1 * base + (g1 < rem ? g1 : rem);
-            for (int i = threadIdx.x; i < (row_hi - row_lo) * M; i += blockDim.x) {
-                const int row = row_lo + i / M, t = i % M;
+        // Every block of the cluster has left its partial sums in the first block's shared memory once the cluster
+        // barrier completes; that block adds them in the order of the column ranges and owns the outputs.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (kpart == 0 && threadIdx.x < kWarps * kMaxTok) {
+            const int w = threadIdx.x / kMaxTok, t = threadIdx.x % kMaxTok, g = group * kWarps + w;
+            const int row = g * base + (g < rem ? g : rem);
+            if (t < M && base + (g < rem ? 1 : 0) > 0) {
                 float sum = 0.0f;
-                for (int k = 0; k < k_split; ++k) sum += __ldcg(a.split_partial + static_cast<size_t>(k * M + t) * a.rows + row);
+                for (int k = 0; k < k_split; ++k) sum += s_split[k][w][t];
                 sum *= StepT::kOutScale;
                 const RowHome h = home_of(a, row);
                 if (h.y != nullptr) h.y[static_cast<size_t>(t) * h.rows + h.local] = sum;
@@ -429,7 +436,6 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                     for (int p = 0; p < a.push.n_ranks; ++p) reinterpret_cast<float *>(a.push.region[p] + h.dst_off)[at] = sum;
                 }
             }
-            if (threadIdx.x == 0) a.split_counters[group] = 0;
         }
     }
 

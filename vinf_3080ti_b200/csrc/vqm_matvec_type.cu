@@ -60,11 +60,22 @@ struct Variant {
             cfg.blockDim = dim3(kWarps * 32);
             cfg.dynamicSmemBytes = kSmem;
             cfg.stream = stream;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cudaLaunchAttribute attr[2];
+            int n_attr = 0;
+            if (a.overlap_launch) {
+                attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+                ++n_attr;
+            }
+            if (a.k_split > 1) {  // the blocks that share a group of rows form a cluster
+                attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+                attr[n_attr].val.clusterDim.x = static_cast<unsigned>(a.k_split);
+                attr[n_attr].val.clusterDim.y = 1;
+                attr[n_attr].val.clusterDim.z = 1;
+                ++n_attr;
+            }
             cfg.attrs = attr;
-            cfg.numAttrs = a.overlap_launch ? 1 : 0;
+            cfg.numAttrs = n_attr;
             return cudaLaunchKernelEx(&cfg, qmv_kernel<VQM_TYPE, M, RW>, a);
         } else {
             return cudaErrorInvalidConfiguration;
@@ -74,17 +85,15 @@ struct Variant {
 
 // Column split for short launches.  When the rows cover less than half of the warps a full grid has (two blocks per SM
 // of kWarps warps - a nominal figure, so that the choice never depends on M and an M-row pass stays equal to M
-// single-row passes bit for bit), every row goes to one warp of a group and k blocks per group share the column
-// segments: k = warps / rows, at most kMaxSplit and at most one block per segment.
+// single-row passes bit for bit), every row goes to one warp of a group and k blocks per group share the columns
+// (evenly, in units of 256): k = warps / rows, at most kMaxSplit (a portable cluster) and at most one block per unit.
 inline int choose_split(const MatvecArgs &a, int sm_count) {
-    if (a.split_partial == nullptr || a.out_idx != nullptr) return 1;
-    const int warps = sm_count * 2 * kWarps, n_seg = (a.cols + kSegCols - 1) / kSegCols;
+    if (!a.allow_split || a.out_idx != nullptr) return 1;
+    const int warps = sm_count * 2 * kWarps, n_units = (a.cols + 255) / 256;
     if (a.rows * 2 > warps) return 1;
     int k = warps / a.rows;
     if (k > kMaxSplit) k = kMaxSplit;
-    if (k > n_seg) k = n_seg;
-    if ((a.rows + kWarps - 1) / kWarps > kSplitGroups) return 1;
-    if (static_cast<long long>(k) * kMaxTok * a.rows > a.split_capacity) return 1;
+    if (k > n_units) k = n_units;
     return k;
 }
 

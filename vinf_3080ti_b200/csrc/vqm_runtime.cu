@@ -78,8 +78,7 @@ struct vqm_runtime {
     int *part_idx = nullptr;
     int *argmax_ids = nullptr;     // [256]: fused argmax uses the first 8, argmax_rows up to 256
     float *argmax_vals = nullptr;  // [8]
-    float *split_partial = nullptr;      // column-split launches: partial sums [k][M][rows]
-    unsigned *split_counters = nullptr;  // ... and one arrival counter per row group
+    int allow_split = 1;  // short launches may be split by columns (VINF_B200_NO_SPLIT=1 turns it off)
     // scratch of the synchronous matvec entry
     float *scratch_x = nullptr, *scratch_y = nullptr;
     size_t scratch_x_n = 0, scratch_y_n = 0;
@@ -176,8 +175,6 @@ int check_shape(const char *name, int type, int cols, int rows, size_t *row_byte
     return VQM_OK;
 }
 
-constexpr int kSplitPartialFloats = vqm::kMaxSplit * 8 * 2048;  // k ranges x 8 activation rows x rows of a short launch
-
 void set_single_part(vqm::MatvecArgs &a, const uint8_t *w, float *y, int rows) {
     for (int i = 0; i < vqm::kMaxParts; ++i) a.part[i] = vqm::MatvecPart{nullptr, nullptr, INT_MAX, 0};
     a.part[0] = vqm::MatvecPart{w, y, rows, rows};
@@ -213,9 +210,7 @@ int launch_parts(vqm_runtime *rt, int n, const Tensor *const *ts, const float *x
     a.row_bytes = static_cast<long long>(t0.row_bytes);
     a.overlap_launch = rt->overlap_launch;
     a.max_grid = vqm::kMaxGrid;
-    a.split_partial = rt->split_partial;
-    a.split_counters = rt->split_counters;
-    a.split_capacity = kSplitPartialFloats;
+    a.allow_split = rt->allow_split;
     if (push != nullptr) {
         a.push = *push;
         a.done_counter = rt->done_counter;
@@ -293,9 +288,6 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
     if (err == cudaSuccess) err = cudaMalloc(&rt->part_idx, sizeof(int) * 8 * vqm::kMaxGrid);
     if (err == cudaSuccess) err = cudaMalloc(&rt->argmax_ids, sizeof(int) * 256);
     if (err == cudaSuccess) err = cudaMalloc(&rt->argmax_vals, sizeof(float) * 8);
-    if (err == cudaSuccess) err = cudaMalloc(&rt->split_partial, sizeof(float) * kSplitPartialFloats);
-    if (err == cudaSuccess) err = cudaMalloc(&rt->split_counters, sizeof(unsigned) * vqm::kSplitGroups);
-    if (err == cudaSuccess) err = cudaMemset(rt->split_counters, 0, sizeof(unsigned) * vqm::kSplitGroups);
     if (err != cudaSuccess) {
         const int rc = cuda_fail("runtime setup", err);
         vqm_runtime_destroy(rt);
@@ -303,10 +295,7 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
     }
     rt->done_counter = rt->status + 16;
     if (const char *e = getenv("VINF_B200_NO_PDL"); e != nullptr && e[0] == '1') rt->overlap_launch = 0;
-    if (const char *e = getenv("VINF_B200_NO_SPLIT"); e != nullptr && e[0] == '1') {  // never split short launches by columns
-        cudaFree(rt->split_partial);
-        rt->split_partial = nullptr;
-    }
+    if (const char *e = getenv("VINF_B200_NO_SPLIT"); e != nullptr && e[0] == '1') rt->allow_split = 0;
     if (iq3s_grid != nullptr) {
         const int rc = vqm_set_codebook(rt, "iq3s_grid", iq3s_grid, nbytes);
         if (rc != VQM_OK) {
@@ -332,8 +321,6 @@ void vqm_runtime_destroy(vqm_runtime *rt) {
     cudaFree(rt->part_idx);
     cudaFree(rt->argmax_ids);
     cudaFree(rt->argmax_vals);
-    cudaFree(rt->split_partial);
-    cudaFree(rt->split_counters);
     cudaFree(rt->scratch_x);
     cudaFree(rt->scratch_y);
     cudaFree(rt->gemm_x);
@@ -922,6 +909,11 @@ int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char 
     p.wait_slot = wait_slot + 1;
     p.wait_lag = wait_lag;
     return launch_group(rt, *t, xp, yp, ntok, with_argmax != 0, &p);
+}
+
+int vqm_set_column_split(vqm_runtime *rt, int enabled) {
+    rt->allow_split = enabled != 0;
+    return VQM_OK;
 }
 
 int vqm_qmv_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok) {

@@ -302,6 +302,11 @@ class Runtime:
         _capi.check(self._lib.vqm_qmv_push(self._h, _name(weight), _name(x), _name(y), int(ntok), int(slot), int(dst_off), int(rows_total),
                                            int(row_begin), int(wait_slot), int(wait_lag), int(with_argmax)))
 
+    def set_column_split(self, enabled: bool) -> None:
+        """Short launches share each row's columns among the blocks of a cluster (default on); off makes a tensor's
+        outputs independent of what else is in its launch."""
+        _capi.check(self._lib.vqm_set_column_split(self._h, int(bool(enabled))))
+
     def qmv_group(self, weights: list[str], x: str, ys: list[str], ntok: int) -> None:
         """ys[i] = W_i x for up to four tensors that share x, their GGUF type and their columns, in ONE launch
         (q/k/v of an attention layer, gate/up of an FFN).  No counterpart in the reference, which launches one
