@@ -337,20 +337,18 @@ def run_gpu(args) -> None:
                 last_of_kind[kind_of(e[0])] = i
 
         def push_pass() -> None:
-            rt.exchange_next_pass()
             for i, group in enumerate(launches_of_pass):
                 cols = group[0][3]
                 slot = i if push_mode != "none" else -1
                 wait_slot = wait_for[i] if push_mode == "full" else -1
-                lag = 1 if wait_for[i] >= i else 0
                 if len(group) == 1:
                     name, t, rows, _ = group[0]
                     rt.qmv_push(name, f"x{cols}", f"y.{kind_of(name)}", m, slot=slot, dst_off=kinds[kind_of(name)], rows_total=rows,
-                                row_begin=local_rows[name][0], wait_slot=wait_slot, wait_lag=lag, with_argmax=(i == len(launches_of_pass) - 1))
+                                row_begin=local_rows[name][0], wait_slot=wait_slot, with_argmax=(i == len(launches_of_pass) - 1))
                 else:
                     rt.qmv_push_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m, slot=slot,
                                       dst_offs=[kinds[kind_of(e[0])] for e in group], rows_totals=[e[2] for e in group],
-                                      row_begins=[local_rows[e[0]][0] for e in group], wait_slot=wait_slot, wait_lag=lag)
+                                      row_begins=[local_rows[e[0]][0] for e in group], wait_slot=wait_slot)
 
         push_pass()
         rt.synchronize()
@@ -392,17 +390,31 @@ def run_gpu(args) -> None:
             ms = float(tmax.item())
         return ms
 
+    # global argmax of a sharded LM head: every rank's (value, index) pairs are all-gathered on the device, one small
+    # device -> host copy, then highest value wins, lowest index on ties
+    if world > 1:
+        pair = torch.zeros((2, 8), dtype=torch.float32, device=dev)   # row 0: values, row 1: the int32 ids' bits
+        pairs = torch.zeros((world, 2, 8), dtype=torch.float32, device=dev)
+        pairs_host = torch.zeros((world, 2, 8), dtype=torch.float32).pin_memory()
+        rt.bind("argmax.pair", pair.data_ptr(), 16)
+        rt.bind("argmax.vals", vals_addr, 8)
+        rt.bind("argmax.ids", ids_addr, 8)
+
     def e2e_step() -> None:
         with torch.cuda.stream(stream):
             for w in widths:
                 dev_x[w].copy_(host_x[w].view(-1), non_blocking=True)
         device_pass()
-        ids, vals = rt.argmax_fetch(m, with_values=True)
-        if world > 1:  # global argmax: all-gather of (value, index) pairs, highest value wins, lowest index on ties
-            pair = torch.tensor([vals, [float(i) for i in ids]], dtype=torch.float64, device=dev)
-            pairs = torch.empty((world, 2, m), dtype=torch.float64, device=dev)
+        if world == 1:
+            rt.argmax_fetch(m, with_values=True)
+            return
+        rt.copy("argmax.pair", 0, "argmax.vals", 0, m)
+        rt.copy("argmax.pair", 8, "argmax.ids", 0, m)
+        with torch.cuda.stream(stream):
             dist.all_gather_into_tensor(pairs, pair)
-            pick_best(pairs[:, 0, :], pairs[:, 1, :].to(torch.int64)).tolist()
+            pairs_host.copy_(pairs, non_blocking=True)
+        stream.synchronize()
+        pick_best(pairs_host[:, 0, :m].to(torch.float64), pairs_host[:, 1, :m].contiguous().view(torch.int32).to(torch.int64)).tolist()
 
     # -- warm-up, then the timed regions
     for _ in range(max(3, args.warmup)):
@@ -447,7 +459,7 @@ def run_gpu(args) -> None:
                                         "and waits for the flags of the launch that produced its input (decoder dependency chain); one CUDA graph per rank, no collective" if use_push else
                                         f"output rows sharded over {world} GPUs, NCCL all-gather after every matvec, eager launches")},
             "tokens_per_s": m / (ms * 1e-3), "pct_of_8TBs": 100.0 * value / 8000.0 / world,
-            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * m,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * m if world == 1 else 64 * world,
                     "tokens_per_s": m / (e2e_ms * 1e-3)},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

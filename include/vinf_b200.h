@@ -156,29 +156,30 @@ int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, flo
 
 /* ---- Row-sharded tensors over several GPUs (no counterpart in the reference, which is a single-GPU engine) ----
  * Every rank (one process per GPU) holds a contiguous slice of the rows of each weight tensor.  vqm_qmv_push is
- * qmv on the local slice fused with its all-gather: the last block of the kernel copies the slice into the gathered
- * [ntok][rows_total] layout inside EVERY rank's exchange region with plain stores over NVLink and then raises a
- * flag in every rank; a kernel that consumes the gathered vector waits (bounded) for the flags of all ranks.
- *   vqm_exchange_create   allocates this rank's region and returns its 64-byte CUDA IPC handle
+ * qmv on the local slice fused with its all-gather: the lane that holds an output stores it into the gathered
+ * [ntok][rows_total] layout inside EVERY rank's exchange region (plain stores over NVLink), and every block then adds
+ * its share of 2^16 to the arrival counter of (slot, this rank) in every region; a kernel that consumes the gathered
+ * vector waits (bounded) until each rank's counter shows as many pushes of the slot as this rank has made itself.
+ *   vqm_exchange_create   allocates this rank's region (zeroed) and returns its 64-byte CUDA IPC handle
  *   vqm_exchange_open     maps a peer's region from its handle
  *   vqm_exchange_config   region addresses of all ranks (own included), this rank, and where inside a region the
- *                         flag table (unsigned flags[n_slots][8]) and the pass counter (one unsigned) live
- *   vqm_exchange_next_pass  advances this rank's pass counter on the stream; call once at the start of every pass
+ *                         arrival counters (unsigned flags[n_slots][8]) and this rank's own push counts (unsigned
+ *                         pushes[n_slots]) live
  *   vqm_qmv_push          y = W_slice x on buffers x, y (y: [ntok][rows of the slice]); then, if slot >= 0, push y to
  *                         dst_off inside every region as rows [row_begin, row_begin + rows) of [ntok][rows_total] and
- *                         signal `slot`.  If wait_slot >= 0, x is only read after every rank signalled wait_slot in
- *                         this pass (wait_lag = 0) or in the previous one (wait_lag = 1, used by the first kernel of
- *                         a pass to make sure no rank is still reading the previous pass's vectors).
+ *                         signal `slot`.  If wait_slot >= 0, x is only read after every rank has pushed wait_slot as
+ *                         often as this rank has: the launch that produced x when it precedes this one in the pass,
+ *                         or - for the first kernel of a pass, waiting on the slot of the pass's last kernel - the
+ *                         previous pass, which makes sure no rank is still reading the vectors about to be rewritten.
  *                         with_argmax: also run the fused argmax (ids offset by the tensor's argmax row base).
- * All ranks must issue the same sequence of pushes per pass.  A wait that expires sets the status word
- * (reported by vqm_synchronize) instead of hanging. */
+ * All ranks must issue the same sequence of pushes.  A wait that expires sets the status word (reported by
+ * vqm_synchronize) instead of hanging. */
 int vqm_exchange_create(vqm_runtime *rt, size_t bytes, void *ipc_handle_out, uint64_t *addr);
 int vqm_exchange_open(vqm_runtime *rt, const void *ipc_handle, uint64_t *addr);
-int vqm_exchange_config(vqm_runtime *rt, int n_ranks, int rank, const uint64_t *region_addrs, size_t flag_off, size_t epoch_off,
+int vqm_exchange_config(vqm_runtime *rt, int n_ranks, int rank, const uint64_t *region_addrs, size_t flag_off, size_t count_off,
                         int n_slots);
-int vqm_exchange_next_pass(vqm_runtime *rt);
 int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int slot, size_t dst_off, int rows_total,
-                 int row_begin, int wait_slot, int wait_lag, int with_argmax);
+                 int row_begin, int wait_slot, int with_argmax);
 
 /* ---- Several tensors in one launch (no counterpart in the reference, which launches one kernel per tensor) ----
  * Tensors that read the same activations, share their GGUF type and have the same number of columns - the q/k/v
@@ -199,7 +200,7 @@ int vqm_qmv_group(vqm_runtime *rt, int n, const char *const *weights, const char
  * VINF_B200_NO_SPLIT=1 sets the default to off.) */
 int vqm_set_column_split(vqm_runtime *rt, int enabled);
 int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok, int slot,
-                       const size_t *dst_offs, const int *rows_totals, const int *row_begins, int wait_slot, int wait_lag);
+                       const size_t *dst_offs, const int *rows_totals, const int *row_begins, int wait_slot);
 
 /* No counterpart in the reference.  The LM-head matvec with fused argmax (like vqm_qmv_argmax) for callers that
  * must not allocate device memory - code inside a no-allocation region of a serving loop, a process whose GPU

@@ -1,6 +1,6 @@
 """The fused matvec + all-gather (qmv_push) on ONE GPU: two runtimes play two ranks that share the device, run one after
 the other (a rank never waits for a flag that has not been raised yet, except in the last test, which lets a bounded
-wait run out on purpose and checks that it is reported instead of hanging)."""
+wait run out on purpose - one rank pushes a slot the other never pushes - and checks that it is reported instead of hanging)."""
 from __future__ import annotations
 
 import numpy as np
@@ -27,7 +27,7 @@ def two_ranks(codebooks):
     rts = [Runtime(codebooks["iq3s_grid"], codebooks) for _ in range(2)]
     addrs = [rt.exchange_create(layout.total)[1] for rt in rts]
     for rank, rt in enumerate(rts):
-        rt.exchange_config(rank, addrs, layout.flag_off, layout.epoch_off, layout.n_slots)
+        rt.exchange_config(rank, addrs, layout.flag_off, layout.count_off, layout.n_slots)
         rt.bind("gathered", addrs[rank], m * rows)                       # slot 0's vector, [m][rows]
         rt.bind("gathered2", addrs[rank] + 4 * m * rows, m * rows2)      # slot 1's vector
         rt.bind("flags", addrs[rank] + layout.flag_off, layout.n_slots * 8)
@@ -49,17 +49,16 @@ def test_push_gathers_slices_on_every_rank_and_chains(two_ranks, codebooks):
         rt.alloc("x", m * cols)
         rt.alloc("y", m * (e - b))
         rt.write("x", x)
-    for epoch in (1, 2):  # two passes: the flags carry the pass number
+    for epoch in (1, 2):  # two passes: every push of a slot adds 2^16 to its arrival counters
         for rank, rt in enumerate(rts):
             b, e = shard_rows(rows, rank, 2)
-            rt.exchange_next_pass()
             rt.qmv_push("w", "x", "y", m, slot=0, dst_off=0, rows_total=rows, row_begin=b)
             rt.synchronize()
         for rt in rts:
             got = rt.read_array("gathered").reshape(m, rows)
             assert rel_l2(got, ref) <= 1e-5
             flags = np.frombuffer(rt.read("flags"), dtype=np.uint32).reshape(layout.n_slots, 8)
-            assert list(flags[0, :2]) == [epoch, epoch] and not flags[1:].any()
+            assert list(flags[0, :2]) == [epoch << 16, epoch << 16] and not flags[1:].any()
     # a consumer whose input is the gathered vector: the flags of slot 0 are already up, so its wait passes at once
     x2 = rts[0].read_array("gathered").reshape(m, rows)[:, : rows - 8].copy()
     ref2 = O.matvec(raw2, int(T.Q4_K), rows2, rows - 8, x2, codebooks)
@@ -92,7 +91,6 @@ def test_push_of_a_group_launch_fills_both_gathered_vectors(two_ranks, codebooks
         rt.alloc("ya", m * (ea - ba))
         rt.alloc("yb", m * (eb - bb))
         rt.write("x", x)
-        rt.exchange_next_pass()
         rt.qmv_push_group(["wa", "wb"], "x", ["ya", "yb"], m, slot=0, dst_offs=[0, 4 * m * rows], rows_totals=[rows, rows2],
                           row_begins=[ba, bb])
         rt.synchronize()
@@ -101,7 +99,7 @@ def test_push_of_a_group_launch_fills_both_gathered_vectors(two_ranks, codebooks
         assert rel_l2(rt.read_array("gathered").reshape(m, rows), ref_a) <= 1e-5
         assert rel_l2(rt.read_array("gathered2").reshape(m, rows2), ref_b) <= 1e-5
         flags = np.frombuffer(rt.read("flags"), dtype=np.uint32).reshape(layout.n_slots, 8)
-        assert list(flags[0, :2]) == [1, 1]
+        assert list(flags[0, :2]) == [1 << 16, 1 << 16]
 
 
 def test_push_with_fused_argmax_reports_global_rows(two_ranks, codebooks):
@@ -118,7 +116,6 @@ def test_push_with_fused_argmax_reports_global_rows(two_ranks, codebooks):
         rt.alloc("x", m * cols)
         rt.alloc("y", m * (e - b))
         rt.write("x", x)
-        rt.exchange_next_pass()
         rt.qmv_push("w", "x", "y", m, slot=0, dst_off=0, rows_total=rows, row_begin=b, with_argmax=True)
         best.append(rt.argmax_fetch(m, with_values=True))
     import torch
@@ -136,8 +133,9 @@ def test_a_wait_that_nothing_satisfies_runs_out_and_is_reported(two_ranks):
     rt.upload("w", synthetic_blocks(T.Q8_0, 64, 256, rng), int(T.Q8_0), 256, 64)
     rt.alloc("x", m * 256)
     rt.alloc("y", m * 64)
-    rt.exchange_next_pass()
-    rt.qmv_push("w", "x", "y", m, slot=-1, dst_off=0, rows_total=64, row_begin=0, wait_slot=2)  # slot 2 is never signalled
+    rt.qmv_push("w", "x", "y", m, slot=2, dst_off=0, rows_total=64, row_begin=0)  # this rank pushes slot 2, the other never does
+    rt.synchronize()
+    rt.qmv_push("w", "x", "y", m, slot=-1, dst_off=0, rows_total=64, row_begin=0, wait_slot=2)
     with pytest.raises(RuntimeError, match="status 2"):
         rt.synchronize()
     rt.qmv("w", "x", "y", m)  # the context is still usable

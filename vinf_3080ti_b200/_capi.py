@@ -71,12 +71,11 @@ SIGNATURES: dict[str, list] = {
     "vqm_exchange_create": [c_void_p, c_size_t, c_void_p, POINTER(c_uint64)],
     "vqm_exchange_open": [c_void_p, c_void_p, POINTER(c_uint64)],
     "vqm_exchange_config": [c_void_p, c_int, c_int, POINTER(c_uint64), c_size_t, c_size_t, c_int],
-    "vqm_exchange_next_pass": [c_void_p],
-    "vqm_qmv_push": [c_void_p, c_char_p, c_char_p, c_char_p, c_int, c_int, c_size_t, c_int, c_int, c_int, c_int, c_int],
+    "vqm_qmv_push": [c_void_p, c_char_p, c_char_p, c_char_p, c_int, c_int, c_size_t, c_int, c_int, c_int, c_int],
     "vqm_set_column_split": [c_void_p, c_int],
     "vqm_qmv_group": [c_void_p, c_int, POINTER(c_char_p), c_char_p, POINTER(c_char_p), c_int],
     "vqm_qmv_push_group": [c_void_p, c_int, POINTER(c_char_p), c_char_p, POINTER(c_char_p), c_int, c_int, POINTER(c_size_t),
-                           POINTER(c_int), POINTER(c_int), c_int, c_int],
+                           POINTER(c_int), POINTER(c_int), c_int],
     "vqm_qmv_raw": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "vqm_qmv_argmax_static": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }

@@ -79,14 +79,7 @@ cudaError_t launch_dequant_t(const uint8_t *w, float *out, long long numel, cons
     return cudaGetLastError();
 }
 
-__global__ void epoch_advance_kernel(unsigned *epoch) { *epoch += 1u; }
-
 }  // namespace
-
-cudaError_t launch_epoch_advance(unsigned *epoch, cudaStream_t stream) {
-    epoch_advance_kernel<<<1, 1, 0, stream>>>(epoch);
-    return cudaGetLastError();
-}
 
 cudaError_t launch_argmax_rows(const float *x, int n, int ntok, int *out, cudaStream_t stream) {
     argmax_rows_kernel<<<ntok, 1024, 0, stream>>>(x, n, out);

@@ -13,15 +13,15 @@ constexpr int kMaxParts = 4;  // tensors one launch can cover (they share the ac
 // stores over NVLink, issued by the lane that holds the output) and which flags order that against the consumers.
 struct PushInfo {
     unsigned long long region[8];  // device address of every rank's exchange region, this rank's included
-    const unsigned *epoch;         // this rank's pass counter (device memory, advanced once per pass)
+    unsigned *pushes;              // this rank's own count of pushes per slot, unsigned[n_slots] (inside its region)
     long long dst_off[kMaxParts];  // per tensor: byte offset, inside a region, of its gathered y[0][0]
-    long long flag_off;            // byte offset, inside a region, of the flag table: unsigned flags[slot][8 ranks]
+    long long flag_off;            // byte offset, inside a region, of the arrival counters: unsigned flags[slot][8 ranks];
+                                   // every push of (slot, rank) adds 2^16 to that counter in every region
     int n_ranks, rank;
     int rows_total[kMaxParts];     // per tensor: the gathered tensor has rows_total rows ...
     int row_begin[kMaxParts];      // ... and this rank's slice starts at row_begin
     int push_slot;                 // 1 + flag slot signalled after the push (0: no push)
-    int wait_slot;                 // 1 + flag slot every rank must have signalled before x is read (0: no wait)
-    int wait_lag;                  // the wait is for epoch - wait_lag (1: the slot was signalled in the previous pass)
+    int wait_slot;                 // 1 + slot every rank must have pushed as often as this rank before x is read (0: no wait)
 };
 
 // One tensor of a launch.  The launch numbers the rows of its tensors consecutively; tensor p owns launch rows
@@ -79,7 +79,6 @@ cudaError_t launch_f32_to_f16_rows(const float *x, void *xh, long long n_valid, 
 cudaError_t launch_qgemm(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
                          const uint8_t *codebook, cudaStream_t stream);
 
-cudaError_t launch_epoch_advance(unsigned *epoch, cudaStream_t stream);
 cudaError_t launch_argmax_rows(const float *x, int n, int ntok, int *out, cudaStream_t stream);
 cudaError_t launch_dequant(int type, const uint8_t *w, float *out, long long numel, const uint8_t *codebook,
                            cudaStream_t stream);

@@ -87,7 +87,7 @@ struct vqm_runtime {
     // exchange of row-sharded outputs between ranks
     void *exchange_own = nullptr;           // region this runtime allocated
     std::vector<void *> exchange_opened;    // peers' regions mapped through IPC handles
-    vqm::PushInfo push{};                   // regions, rank, flag table, epoch
+    vqm::PushInfo push{};                   // regions, rank, counters
     int exchange_slots = 0;
     int gemm_min_rows = 0;
     int overlap_launch = 1;  // programmatic dependent launch of consecutive matvecs (VINF_B200_NO_PDL=1 turns it off)
@@ -857,11 +857,11 @@ int vqm_exchange_open(vqm_runtime *rt, const void *ipc_handle, uint64_t *addr) {
     return VQM_OK;
 }
 
-int vqm_exchange_config(vqm_runtime *rt, int n_ranks, int rank, const uint64_t *region_addrs, size_t flag_off, size_t epoch_off,
+int vqm_exchange_config(vqm_runtime *rt, int n_ranks, int rank, const uint64_t *region_addrs, size_t flag_off, size_t count_off,
                         int n_slots) {
     if (n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks || region_addrs == nullptr || n_slots < 1)
         return fail(VQM_ERR_VALUE, "exchange_config: 1..8 ranks, 0 <= rank < ranks, at least one slot");
-    if ((flag_off & 3u) != 0 || (epoch_off & 3u) != 0) return fail(VQM_ERR_VALUE, "flag and epoch offsets must be 4-byte aligned");
+    if ((flag_off & 3u) != 0 || (count_off & 3u) != 0) return fail(VQM_ERR_VALUE, "flag and count offsets must be 4-byte aligned");
     vqm::PushInfo p{};
     for (int i = 0; i < n_ranks; ++i) {
         if (region_addrs[i] == 0 || (region_addrs[i] & 15u) != 0) return fail(VQM_ERR_VALUE, "region %d is not a 16-byte aligned address", i);
@@ -870,25 +870,17 @@ int vqm_exchange_config(vqm_runtime *rt, int n_ranks, int rank, const uint64_t *
     p.n_ranks = n_ranks;
     p.rank = rank;
     p.flag_off = static_cast<long long>(flag_off);
-    p.epoch = reinterpret_cast<const unsigned *>(region_addrs[rank] + epoch_off);
+    p.pushes = reinterpret_cast<unsigned *>(region_addrs[rank] + count_off);
     rt->push = p;
     rt->exchange_slots = n_slots;
     return VQM_OK;
 }
 
-int vqm_exchange_next_pass(vqm_runtime *rt) {
-    if (rt->push.n_ranks == 0) return fail(VQM_ERR_VALUE, "exchange_config has not been called");
-    const cudaError_t err = vqm::launch_epoch_advance(const_cast<unsigned *>(rt->push.epoch), rt->stream);
-    if (err != cudaSuccess) return cuda_fail("epoch advance", err);
-    count_launch(rt);
-    return VQM_OK;
-}
-
 int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int slot, size_t dst_off, int rows_total,
-                 int row_begin, int wait_slot, int wait_lag, int with_argmax) {
+                 int row_begin, int wait_slot, int with_argmax) {
     if (rt->push.n_ranks == 0) return fail(VQM_ERR_VALUE, "exchange_config has not been called");
     if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8]");
-    if (slot < -1 || slot >= rt->exchange_slots || wait_slot < -1 || wait_slot >= rt->exchange_slots || wait_lag < 0 || wait_lag > 1)
+    if (slot < -1 || slot >= rt->exchange_slots || wait_slot < -1 || wait_slot >= rt->exchange_slots)
         return fail(VQM_ERR_VALUE, "slot out of range");
     int rc = VQM_OK;
     Tensor *t = find_tensor(rt, weight, &rc);
@@ -907,7 +899,6 @@ int vqm_qmv_push(vqm_runtime *rt, const char *weight, const char *x, const char 
     p.row_begin[0] = row_begin;
     p.push_slot = slot + 1;
     p.wait_slot = wait_slot + 1;
-    p.wait_lag = wait_lag;
     return launch_group(rt, *t, xp, yp, ntok, with_argmax != 0, &p);
 }
 
@@ -928,10 +919,10 @@ int vqm_qmv_group(vqm_runtime *rt, int n, const char *const *weights, const char
 }
 
 int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const char *x, const char *const *ys, int ntok, int slot,
-                       const size_t *dst_offs, const int *rows_totals, const int *row_begins, int wait_slot, int wait_lag) {
+                       const size_t *dst_offs, const int *rows_totals, const int *row_begins, int wait_slot) {
     if (rt->push.n_ranks == 0) return fail(VQM_ERR_VALUE, "exchange_config has not been called");
     if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8]");
-    if (slot < -1 || slot >= rt->exchange_slots || wait_slot < -1 || wait_slot >= rt->exchange_slots || wait_lag < 0 || wait_lag > 1)
+    if (slot < -1 || slot >= rt->exchange_slots || wait_slot < -1 || wait_slot >= rt->exchange_slots)
         return fail(VQM_ERR_VALUE, "slot out of range");
     if (dst_offs == nullptr || rows_totals == nullptr || row_begins == nullptr) return fail(VQM_ERR_VALUE, "null pointer");
     const Tensor *ts[vqm::kMaxParts];
@@ -951,7 +942,6 @@ int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const
     }
     p.push_slot = slot + 1;
     p.wait_slot = wait_slot + 1;
-    p.wait_lag = wait_lag;
     return launch_parts(rt, n, ts, xp, yps, ntok, false, &p);
 }
 

@@ -289,18 +289,15 @@ class Runtime:
         _capi.check(self._lib.vqm_exchange_open(self._h, buf, ctypes.byref(addr)))
         return addr.value
 
-    def exchange_config(self, rank: int, region_addrs: Sequence[int], flag_off: int, epoch_off: int, n_slots: int) -> None:
+    def exchange_config(self, rank: int, region_addrs: Sequence[int], flag_off: int, count_off: int, n_slots: int) -> None:
         arr = (ctypes.c_uint64 * len(region_addrs))(*region_addrs)
-        _capi.check(self._lib.vqm_exchange_config(self._h, len(region_addrs), int(rank), arr, int(flag_off), int(epoch_off), int(n_slots)))
-
-    def exchange_next_pass(self) -> None:
-        _capi.check(self._lib.vqm_exchange_next_pass(self._h))
+        _capi.check(self._lib.vqm_exchange_config(self._h, len(region_addrs), int(rank), arr, int(flag_off), int(count_off), int(n_slots)))
 
     def qmv_push(self, weight: str, x: str, y: str, ntok: int, slot: int, dst_off: int, rows_total: int, row_begin: int,
-                 wait_slot: int = -1, wait_lag: int = 0, with_argmax: bool = False) -> None:
+                 wait_slot: int = -1, with_argmax: bool = False) -> None:
         """qmv on this rank's row slice fused with its all-gather (see include/vinf_b200.h)."""
         _capi.check(self._lib.vqm_qmv_push(self._h, _name(weight), _name(x), _name(y), int(ntok), int(slot), int(dst_off), int(rows_total),
-                                           int(row_begin), int(wait_slot), int(wait_lag), int(with_argmax)))
+                                           int(row_begin), int(wait_slot), int(with_argmax)))
 
     def set_column_split(self, enabled: bool) -> None:
         """Short launches share each row's columns among the blocks of a cluster (default on); off makes a tensor's
@@ -319,7 +316,7 @@ class Runtime:
         _capi.check(self._lib.vqm_qmv_group(self._h, n, w, _name(x), y, int(ntok)))
 
     def qmv_push_group(self, weights: list[str], x: str, ys: list[str], ntok: int, slot: int, dst_offs: list[int],
-                       rows_totals: list[int], row_begins: list[int], wait_slot: int = -1, wait_lag: int = 0) -> None:
+                       rows_totals: list[int], row_begins: list[int], wait_slot: int = -1) -> None:
         """qmv_group on this rank's row slices fused with their all-gathers: one flag slot for the launch."""
         n = len(weights)
         if not (len(ys) == len(dst_offs) == len(rows_totals) == len(row_begins) == n):
@@ -327,8 +324,7 @@ class Runtime:
         w = (ctypes.c_char_p * n)(*[_name(v) for v in weights])
         y = (ctypes.c_char_p * n)(*[_name(v) for v in ys])
         _capi.check(self._lib.vqm_qmv_push_group(self._h, n, w, _name(x), y, int(ntok), int(slot), (ctypes.c_size_t * n)(*dst_offs),
-                                                 (ctypes.c_int * n)(*rows_totals), (ctypes.c_int * n)(*row_begins), int(wait_slot),
-                                                 int(wait_lag)))
+                                                 (ctypes.c_int * n)(*rows_totals), (ctypes.c_int * n)(*row_begins), int(wait_slot)))
 
     # ---- residency machinery of the reference: everything is resident here ------------------------------
     # (engine/csrc/megakernel/qwen_runtime.cu:1485-1811; engine/src/vinf/gguf/residency.py:256-354)

@@ -61,14 +61,14 @@ def pick_best(values: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
 
 class ExchangeLayout:
     """Byte layout of a rank's exchange region for the fused push (Runtime.qmv_push): gathered vectors first, then
-    the flag table unsigned[n_slots][8], then the pass counter."""
+    the arrival counters unsigned[n_slots][8], then this rank's own push counts unsigned[n_slots]."""
 
     def __init__(self, data_bytes: int, n_slots: int) -> None:
         self.data_bytes = (int(data_bytes) + 255) // 256 * 256
         self.n_slots = int(n_slots)
         self.flag_off = self.data_bytes
-        self.epoch_off = self.flag_off + self.n_slots * 8 * 4
-        self.total = (self.epoch_off + 4 + 255) // 256 * 256
+        self.count_off = self.flag_off + self.n_slots * 8 * 4
+        self.total = (self.count_off + self.n_slots * 4 + 255) // 256 * 256
 
 
 def connect_exchange(rt, layout: ExchangeLayout, group=None) -> list[int]:
@@ -79,6 +79,6 @@ def connect_exchange(rt, layout: ExchangeLayout, group=None) -> list[int]:
     handles: list = [None] * world
     dist.all_gather_object(handles, handle, group=group)
     addrs = [own if k == rank else rt.exchange_open(handles[k]) for k in range(world)]
-    rt.exchange_config(rank, addrs, layout.flag_off, layout.epoch_off, layout.n_slots)
+    rt.exchange_config(rank, addrs, layout.flag_off, layout.count_off, layout.n_slots)
     dist.barrier(group)
     return addrs
