@@ -157,13 +157,14 @@ int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, flo
 /* ---- Row-sharded tensors over several GPUs (no counterpart in the reference, which is a single-GPU engine) ----
  * Every rank (one process per GPU) holds a contiguous slice of the rows of each weight tensor.  vqm_qmv_push is
  * qmv on the local slice fused with its all-gather: the lane that holds an output stores it into the gathered
- * [ntok][rows_total] layout inside EVERY rank's exchange region (plain stores over NVLink), and every block then adds
- * its share of 2^16 to the arrival counter of (slot, this rank) in every region; a kernel that consumes the gathered
- * vector waits (bounded) until each rank's counter shows as many pushes of the slot as this rank has made itself.
+ * [ntok][rows_total] layout inside EVERY rank's exchange region (plain stores over NVLink), and the last block of the
+ * launch to finish writes this rank's push count of the slot into the flag table of every region; a kernel that
+ * consumes the gathered vector waits (bounded) until each rank's flag shows as many pushes of the slot as this rank
+ * has made itself.
  *   vqm_exchange_create   allocates this rank's region (zeroed) and returns its 64-byte CUDA IPC handle
  *   vqm_exchange_open     maps a peer's region from its handle
  *   vqm_exchange_config   region addresses of all ranks (own included), this rank, and where inside a region the
- *                         arrival counters (unsigned flags[n_slots][8]) and this rank's own push counts (unsigned
+ *                         flag table (unsigned flags[n_slots][8]) and this rank's own push counts (unsigned
  *                         pushes[n_slots]) live
  *   vqm_qmv_push          y = W_slice x on buffers x, y (y: [ntok][rows of the slice]); then, if slot >= 0, push y to
  *                         dst_off inside every region as rows [row_begin, row_begin + rows) of [ntok][rows_total] and

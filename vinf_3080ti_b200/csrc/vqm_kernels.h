@@ -15,8 +15,8 @@ struct PushInfo {
     unsigned long long region[8];  // device address of every rank's exchange region, this rank's included
     unsigned *pushes;              // this rank's own count of pushes per slot, unsigned[n_slots] (inside its region)
     long long dst_off[kMaxParts];  // per tensor: byte offset, inside a region, of its gathered y[0][0]
-    long long flag_off;            // byte offset, inside a region, of the arrival counters: unsigned flags[slot][8 ranks];
-                                   // every push of (slot, rank) adds 2^16 to that counter in every region
+    long long flag_off;            // byte offset, inside a region, of the flag table: unsigned flags[slot][8 ranks], the
+                                   // number of pushes of the slot each rank has completed
     int n_ranks, rank;
     int rows_total[kMaxParts];     // per tensor: the gathered tensor has rows_total rows ...
     int row_begin[kMaxParts];      // ... and this rank's slice starts at row_begin

@@ -264,14 +264,13 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (warp == 0 && a.push.wait_slot > 0) {
         // Row-sharded input: x was assembled by pushes from every rank.  Lane p waits (bounded) until rank p has pushed
-        // the slot as often as this rank has (all blocks of its launch: the counter reads pushes << 16) - the counters
-        // are polled in parallel, one L2 round trip when they are already there - then the ranks' stores are made
-        // visible to the bulk copies below.
+        // the slot as often as this rank has - the flags are polled in parallel, one L2 round trip when they are
+        // already up - then the ranks' stores are made visible to the bulk copies below.
         bool ok = *reinterpret_cast<volatile unsigned *>(a.status) == 0;  // after one expiry later kernels do not wait again
         if (lane < a.push.n_ranks && ok) {
             const volatile unsigned *flag = reinterpret_cast<const volatile unsigned *>(a.push.region[a.push.rank] + a.push.flag_off) +
                                             (a.push.wait_slot - 1) * 8 + lane;
-            const unsigned target = *reinterpret_cast<const volatile unsigned *>(a.push.pushes + (a.push.wait_slot - 1)) << 16;
+            const unsigned target = *reinterpret_cast<const volatile unsigned *>(a.push.pushes + (a.push.wait_slot - 1));
             int spins = 0;
             auto acquire = [](const volatile unsigned *p) {
                 unsigned v;
@@ -440,49 +439,40 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
         }
     }
 
-    if (a.push.push_slot > 0) {
-        // Row-sharded output: tell every rank that this block's values have arrived.  The flag of (slot, this rank) in a
-        // rank's table is a counter to which the blocks of a launch add shares that sum to 2^16, so it reads
-        // pushes << 16 once the whole launch has pushed; nobody waits for a last block.  The barrier orders the
-        // block's remote stores before the system-scope fence of the signalling threads (one per rank).
-        __syncthreads();
-        if (blockIdx.x == 0 && threadIdx.x == 32) a.push.pushes[a.push.push_slot - 1] += 1u;  // read by this rank's later kernels
-        if (threadIdx.x < a.push.n_ranks) {
-            __threadfence_system();
-            const unsigned share = 65536u / gridDim.x + (blockIdx.x == 0 ? 65536u % gridDim.x : 0u);
-            unsigned *flag = reinterpret_cast<unsigned *>(a.push.region[threadIdx.x] + a.push.flag_off) + (a.push.push_slot - 1) * 8 + a.push.rank;
-            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(share) : "memory");
-        }
-    }
-
-    if (want_argmax) {
-        // block partials of the argmax, then the last block to finish reduces them
+    const bool want_push = a.push.push_slot > 0;
+    if (want_argmax || want_push) {
+        // block partials of the argmax, then the last block to finish reduces them and / or signals the push
         __shared__ float s_val[kWarps][32];
         __shared__ int s_idx[kWarps][32];
         __shared__ bool s_last;
-        s_val[warp][lane] = best_v;
-        s_idx[warp][lane] = best_i;
-        __syncthreads();
-        if (threadIdx.x < M) {
-            const int t = threadIdx.x;
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-            for (int w = 0; w < kWarps; ++w)
-                for (int r = 0; r < RW; ++r)
-                    if (better(s_val[w][r * M + t], s_idx[w][r * M + t], bv, bi)) {
-                        bv = s_val[w][r * M + t];
-                        bi = s_idx[w][r * M + t];
-                    }
-            a.part_val[t * gridDim.x + blockIdx.x] = bv;
-            a.part_idx[t * gridDim.x + blockIdx.x] = bi;
+        if (want_argmax) {
+            s_val[warp][lane] = best_v;
+            s_idx[warp][lane] = best_i;
+            __syncthreads();
+            if (threadIdx.x < M) {
+                const int t = threadIdx.x;
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                for (int w = 0; w < kWarps; ++w)
+                    for (int r = 0; r < RW; ++r)
+                        if (better(s_val[w][r * M + t], s_idx[w][r * M + t], bv, bi)) {
+                            bv = s_val[w][r * M + t];
+                            bi = s_idx[w][r * M + t];
+                        }
+                a.part_val[t * gridDim.x + blockIdx.x] = bv;
+                a.part_idx[t * gridDim.x + blockIdx.x] = bi;
+            }
         }
+        // Release at GPU scope: this block's stores (remote ones included) happen before its count below; the last
+        // block's system-scope fence is cumulative over everything it has observed through the counter.
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) s_last = atomicAdd(a.done_counter, 1u) == gridDim.x - 1;
         __syncthreads();
         if (s_last) {
-            __threadfence();
-            if (warp < M) {
+            if (want_push) __threadfence_system();
+            else __threadfence();
+            if (want_argmax && warp < M) {
                 const int t = warp;
                 float bv = -INFINITY;
                 int bi = 0x7fffffff;
@@ -507,6 +497,18 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                     a.out_idx[t] = bi == 0x7fffffff ? bi : bi + a.row_base;
                     if (a.out_val != nullptr) a.out_val[t] = bv;
                 }
+            }
+            if (want_push) {
+                // every block made its remote stores visible (system-wide fence above) before it counted itself done:
+                // write this rank's new push count of the slot into every rank's table, then remember it here
+                const unsigned count = a.push.pushes[a.push.push_slot - 1] + 1u;
+                if (threadIdx.x < a.push.n_ranks) {
+                    volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(a.push.region[threadIdx.x] + a.push.flag_off) +
+                                              (a.push.push_slot - 1) * 8 + a.push.rank;
+                    *flag = count;
+                }
+                __syncthreads();
+                if (threadIdx.x == 0) a.push.pushes[a.push.push_slot - 1] = count;
             }
             if (threadIdx.x == 0) *a.done_counter = 0;
         }

@@ -61,7 +61,7 @@ def pick_best(values: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
 
 class ExchangeLayout:
     """Byte layout of a rank's exchange region for the fused push (Runtime.qmv_push): gathered vectors first, then
-    the arrival counters unsigned[n_slots][8], then this rank's own push counts unsigned[n_slots]."""
+    the flag table unsigned[n_slots][8], then this rank's own push counts unsigned[n_slots]."""
 
     def __init__(self, data_bytes: int, n_slots: int) -> None:
         self.data_bytes = (int(data_bytes) + 255) // 256 * 256
