@@ -443,6 +443,8 @@ def run_gpu(args) -> None:
     alg_bytes = d_rows * (dom[0][3] // 256) * 110 + 4 * m * dom[0][3] + 4 * m * d_rows
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (dom_ms * 1e-3) / 1e9
+    # second bound: one fp32 FMA per weight per activation row on 148 SMs x 128 lanes at the maximum SM clock
+    fma_ceiling = 148 * 128 * 1.965e9 / m * (110 / 256) / 1e9  # weight GB/s at which the FMA pipe alone saturates
 
     if rank == 0:
         value = weight_bytes_total / (ms * 1e-3) / 1e9
@@ -463,8 +465,10 @@ def run_gpu(args) -> None:
                     "tokens_per_s": m / (e2e_ms * 1e-3)},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": f"qmv_kernel<Q3_K, M={m}> {d_rows}x{dom[0][3]}",
-                         "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": dom_ms * 1e3, "peak_source": f"of {peak_kind}"},
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (m == 4 and world == 1) else None, "kernel": f"qmv_kernel<Q3_K, M={m}> {d_rows}x{dom[0][3]}",
+                         "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": dom_ms * 1e3, "peak_source": f"of {peak_kind}",
+                         "fp32_fma_ceiling": {"weight_GBs": fma_ceiling, "frac": achieved / min(peak, fma_ceiling),
+                                              "note": "achieved / min(HBM peak, rate at which one FMA per weight per activation row saturates the fp32 pipe)"}},
             "clocks": clocks,
         }
         if cpu is not None:

@@ -475,3 +475,25 @@ def test_group_launch_error_contract(rt):
         rt.qmv_group(["gb", "nope"], "x", ["ya", "yb"], 1)
     with pytest.raises(ValueError):
         rt.qmv_group(["gb"], "x", ["ya"], 9)
+
+
+@pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
+def test_prompt_gemm_tcgen05_matches_the_matvec_path_for_every_type(rt, codebooks, t):
+    """Passes of 128+ activation rows take the tcgen05 kernel (accumulators in tensor memory): 200 x 1024 weights (a
+    partial tile of rows), 130 activation rows (a partial tile of 512), same tolerance as the warp-level kernel."""
+    rng = np.random.default_rng(5100 + int(t))
+    rows, cols, ntok = 200, 1024, 130
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    ref = run_qmv(rt, raw, t, rows, cols, x)  # fp32 matvec, groups of 8
+    rt.set_gemm_min_rows(64)
+    try:
+        rt.zero("y")
+        rt.qmv("w", "x", "y", ntok)
+        rt.synchronize()
+        got = rt.read_array("y").reshape(ntok, rows)
+    finally:
+        rt.set_gemm_min_rows(0)
+    assert np.all(np.abs(got - ref) <= 3e-3 * np.abs(ref).max())
+    oracle = O.matvec(raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, oracle) <= 2e-3  # fp16 rounding of both operands

@@ -69,6 +69,7 @@ def build(force: bool = False, jobs: int | None = None, verbose: bool = False) -
     ]
     work.append(("vqm_aux.cu", [], OBJ / "aux.o"))
     work.append(("vqm_gemm.cu", [], OBJ / "gemm.o"))
+    work.append(("vqm_gemm_tc5.cu", [], OBJ / "gemm_tc5.o"))
     work.append(("vqm_runtime.cu", [], OBJ / "runtime.o"))
     jobs = jobs or min(len(work), os.cpu_count() or 4)
     logs = []

@@ -79,6 +79,13 @@ cudaError_t launch_f32_to_f16_rows(const float *x, void *xh, long long n_valid, 
 cudaError_t launch_qgemm(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
                          const uint8_t *codebook, cudaStream_t stream);
 
+// Prompt-pass GEMM on tcgen05 tensor cores with the accumulators in tensor memory (vqm_gemm_tc5.cu): 512 activation rows
+// per block; needs cols to be a multiple of 64.  status: device word that receives a code if a bounded wait expires.
+int gemm_tc5_token_tile();
+bool gemm_tc5_supports(int cols);
+cudaError_t launch_qgemm_tc5(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
+                             const uint8_t *codebook, unsigned *status, cudaStream_t stream);
+
 cudaError_t launch_argmax_rows(const float *x, int n, int ntok, int *out, cudaStream_t stream);
 cudaError_t launch_dequant(int type, const uint8_t *w, float *out, long long numel, const uint8_t *codebook,
                            cudaStream_t stream);

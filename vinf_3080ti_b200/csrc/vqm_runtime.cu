@@ -90,6 +90,7 @@ struct vqm_runtime {
     vqm::PushInfo push{};                   // regions, rank, counters
     int exchange_slots = 0;
     int gemm_min_rows = 0;
+    int gemm_tcgen05 = 1;    // prompt passes of 128+ rows run on the tcgen05 kernel (VINF_B200_GEMM=mma: warp-level MMA only)
     int overlap_launch = 1;  // programmatic dependent launch of consecutive matvecs (VINF_B200_NO_PDL=1 turns it off)
     bool capturing = false;
     uint64_t launches = 0, capture_launches = 0;
@@ -296,6 +297,7 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
     rt->done_counter = rt->status + 16;
     if (const char *e = getenv("VINF_B200_NO_PDL"); e != nullptr && e[0] == '1') rt->overlap_launch = 0;
     if (const char *e = getenv("VINF_B200_NO_SPLIT"); e != nullptr && e[0] == '1') rt->allow_split = 0;
+    if (const char *e = getenv("VINF_B200_GEMM"); e != nullptr && strcmp(e, "mma") == 0) rt->gemm_tcgen05 = 0;
     if (iq3s_grid != nullptr) {
         const int rc = vqm_set_codebook(rt, "iq3s_grid", iq3s_grid, nbytes);
         if (rc != VQM_OK) {
@@ -595,7 +597,9 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
         const uint8_t *cb = codebook_for(rt, t->type);
         if (vqm::grid_is_codebook(t->type) && cb == nullptr)
             return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t->type);
-        const int tile = vqm::gemm_token_tile();
+        // tcgen05 kernel (512 activation rows per block) from 128 rows on, the warp-level MMA kernel below that
+        const bool tc5 = rt->gemm_tcgen05 && ntok >= 128 && vqm::gemm_tc5_supports(t->cols);
+        const int tile = tc5 ? vqm::gemm_tc5_token_tile() : vqm::gemm_token_tile();
         const size_t need = static_cast<size_t>((ntok + tile - 1) / tile * tile) * t->cols;
         cudaError_t err = cudaSuccess;
         if (need > rt->gemm_x_len) {
@@ -609,8 +613,13 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
             rt->gemm_x_len = need;
         }
         err = vqm::launch_f32_to_f16_rows(xp, rt->gemm_x, static_cast<long long>(ntok) * t->cols, static_cast<long long>(need), rt->stream);
-        if (err == cudaSuccess)
-            err = vqm::launch_qgemm(t->type, t->data, rt->gemm_x, yp, t->rows, t->cols, static_cast<long long>(t->row_bytes), ntok, cb, rt->stream);
+        if (err == cudaSuccess) {
+            if (tc5)
+                err = vqm::launch_qgemm_tc5(t->type, t->data, rt->gemm_x, yp, t->rows, t->cols, static_cast<long long>(t->row_bytes), ntok, cb,
+                                            rt->status, rt->stream);
+            else
+                err = vqm::launch_qgemm(t->type, t->data, rt->gemm_x, yp, t->rows, t->cols, static_cast<long long>(t->row_bytes), ntok, cb, rt->stream);
+        }
         if (err != cudaSuccess) return cuda_fail("qmv gemm launch", err);
         count_launch(rt, 2);
         return VQM_OK;
