@@ -4,13 +4,14 @@
 // engine/csrc/megakernel/qwen_runtime.cu:655-769: fp16 operands, fp32 accumulation), built on tcgen05:
 //   * a block owns 128 weight rows (the MMA's M) and 512 activation rows (two accumulators of N = 256); the fp32
 //     accumulators live in tensor memory (128 lanes x 512 columns, the whole TMEM of an SM, so one block per SM);
-//   * K is walked in stages of 64: warps 0-3 dequantise the 128 x 64 weight tile with the exact block decoders (one
-//     thread per row, 8 chunks of 8 weights) and store it as fp16 in the K-major 128-byte-swizzled layout the tensor
-//     core reads; warps 4-6 copy the 512 x 64 fp16 activation tile into the same layout with cp.async; both sides
-//     make their writes visible to the async proxy and arrive on the stage's "full" mbarrier;
-//   * one thread of warp 7 issues, per stage, 4 K-steps x 2 accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
-//     K = 16) from shared-memory descriptors and commits them to the stage's "empty" mbarrier, which hands the stage
-//     back to the producers; two stages overlap the tile production with the MMAs;
+//   * K is walked in stages of 64, each filled and consumed as two halves of 32 (four pipeline slots in two stage
+//     buffers): warps 0-7 dequantise the 128 x 32 weight half-tile with the exact block decoders (two threads per row,
+//     two chunks of 8 weights each) and store it as fp16 in the K-major 128-byte-swizzled layout the tensor core
+//     reads; warps 8-10 copy the 512 x 32 fp16 activation half-tile into the same layout with cp.async; both sides
+//     make their writes visible to the async proxy and arrive on the slot's "full" mbarrier;
+//   * one thread of warp 11 issues, per slot, 2 K-steps x 2 accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
+//     K = 16) from shared-memory descriptors and commits them to the slot's "empty" mbarrier, which hands the slot
+//     back to the producers, so tile production runs up to three slots ahead of the MMAs;
 //   * after the last commit, warps 0-3 read the accumulators with tcgen05.ld (warp w owns lanes 32w..32w+31, one
 //     weight row per thread) and store y; a warp stores 32 consecutive rows of one activation row, 128 bytes.
 // Every mbarrier wait is bounded: on expiry the block records a status code, everybody falls through to the end, and
@@ -25,8 +26,9 @@ namespace {
 
 constexpr int kTM = 128, kTN = 512, kTK = 64, kTStages = 2;
 constexpr int kTA = kTM * kTK * 2, kTB = kTN * kTK * 2, kTStage = kTA + kTB;  // 16 KB + 64 KB
-constexpr int kTThreads = 256;
-constexpr int kAThreads = 128, kBThreads = 96;
+constexpr int kTSlots = 2 * kTStages;  // half stages
+constexpr int kTThreads = 384;
+constexpr int kAThreads = 256, kBThreads = 96;
 constexpr uint32_t kTmemCols = 512;
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     constexpr int CPB = chunk_block(TYPE) / 8, BB = chunk_block_bytes(TYPE);
     constexpr int TABLE = grid_bytes(TYPE) > 0 ? (grid_bytes(TYPE) + 15) / 16 * 16 : 16;
     extern __shared__ uint8_t tc5_raw[];
-    __shared__ __align__(8) uint64_t s_full[kTStages], s_empty[kTStages], s_done;
+    __shared__ __align__(8) uint64_t s_full[kTSlots], s_empty[kTSlots], s_done;
     __shared__ uint32_t s_tmem;
     __shared__ int s_failed;
     // table first, then the stages on a 1024-byte boundary (the swizzle works on absolute shared-memory address bits)
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     const int n_k = cols / kTK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTStages; ++s) {
+        for (int s = 0; s < kTSlots; ++s) {
             bar_init(s32(&s_full[s]), kAThreads + kBThreads);
             bar_init(s32(&s_empty[s]), 1);
         }
@@ -125,68 +127,73 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     const uint32_t tmem = s_tmem;
     volatile int *failed = &s_failed;
 
-    if (warp < 4) {
-        // ---- weight tile: thread = row; chunk c (8 weights, 16 bytes of fp16) goes to 16-byte slot c ^ (row % 8) of the row
-        const int r = threadIdx.x;
+    const int n_slots = 2 * n_k;  // slot q of the pipeline: stage (q / 2) % 2, K half q % 2
+    if (warp < 8) {
+        // ---- weight half-tile: two threads per row, two chunks each; chunk c of the stage (8 weights, 16 bytes of fp16)
+        //      goes to 16-byte slot c ^ (row % 8) of the row
+        const int r = threadIdx.x & 127, pair = threadIdx.x >> 7;
         const bool valid = row0 + r < rows;
         const uint8_t *w_row = w + static_cast<size_t>(valid ? row0 + r : 0) * row_bytes;
-        for (int it = 0; it < n_k; ++it) {
-            const int s = it % kTStages;
-            if (!bar_wait(s32(&s_empty[s]), ((it / kTStages) & 1) ^ 1, failed)) break;
-            const uint32_t a_row = tiles + s * kTStage + r * 128;
-#pragma unroll 2
-            for (int c = 0; c < kTK / 8; ++c) {
+        for (int q = 0; q < n_slots; ++q) {
+            const int slot = q % kTSlots;
+            if (!bar_wait(s32(&s_empty[slot]), ((q / kTSlots) & 1) ^ 1, failed)) break;
+            const uint32_t a_row = tiles + (slot >> 1) * kTStage + r * 128;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int c = (slot & 1) * 4 + pair * 2 + i;  // chunk within the stage
+                const int kc = (q >> 1) * (kTK / 8) + c;       // chunk within the row
                 float v[8];
-                const int kc = it * (kTK / 8) + c;
                 if (valid) {
                     deq8<TYPE>(w_row + static_cast<size_t>(kc / CPB) * BB, kc % CPB, v, table);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+                    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
                 }
                 __half2 h[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-                const uint4 q = *reinterpret_cast<const uint4 *>(h);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + ((c ^ (r & 7)) << 4)), "r"(q.x), "r"(q.y), "r"(q.z), "r"(q.w)
+                for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+                const uint4 pk = *reinterpret_cast<const uint4 *>(h);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + ((c ^ (r & 7)) << 4)), "r"(pk.x), "r"(pk.y), "r"(pk.z),
+                             "r"(pk.w)
                              : "memory");
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            bar_arrive(s32(&s_full[s]));
+            bar_arrive(s32(&s_full[slot]));
         }
-    } else if (warp < 7) {
-        // ---- activation tile: 512 rows x 8 chunks of 16 bytes, same swizzle; rows beyond ntok exist and are zero
+    } else if (warp < 11) {
+        // ---- activation half-tile: 512 rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist and are zero
         const int b = threadIdx.x - kAThreads;
-        for (int it = 0; it < n_k; ++it) {
-            const int s = it % kTStages;
-            if (!bar_wait(s32(&s_empty[s]), ((it / kTStages) & 1) ^ 1, failed)) break;
-            const uint32_t b_tile = tiles + s * kTStage + kTA;
-            const __half *src = xh + static_cast<size_t>(tok0) * cols + it * kTK;
-            for (int i = b; i < kTN * 8; i += kBThreads) {
-                const int n = i >> 3, c = i & 7;
+        for (int q = 0; q < n_slots; ++q) {
+            const int slot = q % kTSlots;
+            if (!bar_wait(s32(&s_empty[slot]), ((q / kTSlots) & 1) ^ 1, failed)) break;
+            const uint32_t b_tile = tiles + (slot >> 1) * kTStage + kTA;
+            const __half *src = xh + static_cast<size_t>(tok0) * cols + (q >> 1) * kTK + (slot & 1) * 32;
+            for (int i = b; i < kTN * 4; i += kBThreads) {
+                const int n = i >> 2, c = (slot & 1) * 4 + (i & 3);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_tile + n * 128 + ((c ^ (n & 7)) << 4)),
-                             "l"(src + static_cast<size_t>(n) * cols + c * 8)
+                             "l"(src + static_cast<size_t>(n) * cols + (i & 3) * 8)
                              : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            bar_arrive(s32(&s_full[s]));
+            bar_arrive(s32(&s_full[slot]));
         }
     } else if (lane == 0) {
         // ---- MMA issue: accumulator 0 (activation rows 0..255) at column 0, accumulator 1 at column 256
-        for (int it = 0; it < n_k; ++it) {
-            const int s = it % kTStages;
-            if (!bar_wait(s32(&s_full[s]), (it / kTStages) & 1, failed)) break;
+        for (int q = 0; q < n_slots; ++q) {
+            const int slot = q % kTSlots;
+            if (!bar_wait(s32(&s_full[slot]), (q / kTSlots) & 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t a_desc = sw128_desc(tiles + s * kTStage), b_desc = sw128_desc(tiles + s * kTStage + kTA);
+            const uint64_t a_desc = sw128_desc(tiles + (slot >> 1) * kTStage), b_desc = sw128_desc(tiles + (slot >> 1) * kTStage + kTA);
 #pragma unroll
-            for (int j = 0; j < kTK / 16; ++j) {  // 32 bytes further along K inside the swizzled rows per step
-                const uint32_t acc = (it | j) != 0;
+            for (int jj = 0; jj < 2; ++jj) {  // 32 bytes further along K inside the swizzled rows per step
+                const int j = (slot & 1) * 2 + jj;
+                const uint32_t acc = (q | jj) != 0;
                 mma_f16(tmem, a_desc + 2 * j, b_desc + 2 * j, acc);
                 mma_f16(tmem + 256, a_desc + 2 * j, b_desc + 2 * j + ((256 * 128) >> 4), acc);
             }
-            mma_commit(s32(&s_empty[s]));  // the stage is free again once these MMAs have read it
+            mma_commit(s32(&s_empty[slot]));  // the slot is free again once these MMAs have read it
         }
         mma_commit(s32(&s_done));
     }
