@@ -5,11 +5,12 @@
 //   * a block owns 128 weight rows (the MMA's M) and 512 activation rows (two accumulators of N = 256); the fp32
 //     accumulators live in tensor memory (128 lanes x 512 columns, the whole TMEM of an SM, so one block per SM);
 //   * K is walked in stages of 64, each filled and consumed as two halves of 32 (four pipeline slots in two stage
-//     buffers): warps 0-7 dequantise the 128 x 32 weight half-tile with the exact block decoders (two threads per row,
-//     two chunks of 8 weights each) and store it as fp16 in the K-major 128-byte-swizzled layout the tensor core
-//     reads; warps 8-10 copy the 512 x 32 fp16 activation half-tile into the same layout with cp.async; both sides
-//     make their writes visible to the async proxy and arrive on the slot's "full" mbarrier;
-//   * one thread of warp 11 issues, per slot, 2 K-steps x 2 accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
+//     buffers): warps 0-15 dequantise the 128 x 32 weight half-tile with the exact block decoders (four threads per
+//     row, one chunk of 8 weights each) and store it as fp16 in the K-major 128-byte-swizzled layout the tensor core
+//     reads; warps 16-18 copy the 512 x 32 fp16 activation half-tile into the same layout with cp.async (the copies of
+//     three slots in flight per thread); both sides make their writes visible to the async proxy and arrive on the
+//     slot's "full" mbarrier;
+//   * one thread of warp 19 issues, per slot, 2 K-steps x 2 accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
 //     K = 16) from shared-memory descriptors and commits them to the slot's "empty" mbarrier, which hands the slot
 //     back to the producers, so tile production runs up to three slots ahead of the MMAs;
 //   * after the last commit, warps 0-3 read the accumulators with tcgen05.ld (warp w owns lanes 32w..32w+31, one
@@ -27,8 +28,8 @@ namespace {
 constexpr int kTM = 128, kTN = 512, kTK = 64, kTStages = 2;
 constexpr int kTA = kTM * kTK * 2, kTB = kTN * kTK * 2, kTStage = kTA + kTB;  // 16 KB + 64 KB
 constexpr int kTSlots = 2 * kTStages;  // half stages
-constexpr int kTThreads = 384;
-constexpr int kAThreads = 256, kBThreads = 96;
+constexpr int kTThreads = 640;
+constexpr int kAThreads = 512, kBThreads = 96;
 constexpr uint32_t kTmemCols = 512;
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -128,23 +129,28 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     volatile int *failed = &s_failed;
 
     const int n_slots = 2 * n_k;  // slot q of the pipeline: stage (q / 2) % 2, K half q % 2
-    if (warp < 8) {
-        // ---- weight half-tile: two threads per row, two chunks each; chunk c of the stage (8 weights, 16 bytes of fp16)
+    if (warp < 16) {
+        // ---- weight half-tile: four threads per row, one chunk each; chunk c of the stage (8 weights, 16 bytes of fp16)
         //      goes to 16-byte slot c ^ (row % 8) of the row
-        const int r = threadIdx.x & 127, pair = threadIdx.x >> 7;
+        //      (the four threads of a row are neighbours in a warp: their global loads fall into the same sectors)
+        const int r = threadIdx.x >> 2, quarter = threadIdx.x & 3;
         const bool valid = row0 + r < rows;
         const uint8_t *w_row = w + static_cast<size_t>(valid ? row0 + r : 0) * row_bytes;
         for (int q = 0; q < n_slots; ++q) {
             const int slot = q % kTSlots;
             if (!bar_wait(s32(&s_empty[slot]), ((q / kTSlots) & 1) ^ 1, failed)) break;
             const uint32_t a_row = tiles + (slot >> 1) * kTStage + r * 128;
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int c = (slot & 1) * 4 + pair * 2 + i;  // chunk within the stage
-                const int kc = (q >> 1) * (kTK / 8) + c;       // chunk within the row
+            {
+                const int c = (slot & 1) * 4 + quarter;   // chunk within the stage
+                const int kc = (q >> 1) * (kTK / 8) + c;   // chunk within the row
                 float v[8];
                 if (valid) {
-                    deq8<TYPE>(w_row + static_cast<size_t>(kc / CPB) * BB, kc % CPB, v, table);
+                    const uint8_t *blk = w_row + static_cast<size_t>(kc / CPB) * BB;
+                    deq8<TYPE>(blk, kc % CPB, v, table);
+                    // the row's bytes of the next stages: into L2 -> L1 ahead of use (hint only)
+                    constexpr int kAhead = CPB == 32 ? BB : 4 * BB;
+                    if (quarter == 0 && static_cast<long long>(kc / CPB) * BB + kAhead < row_bytes)
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(blk + kAhead));
                 } else {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) v[e] = 0.0f;
@@ -160,14 +166,20 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             bar_arrive(s32(&s_full[slot]));
         }
-    } else if (warp < 11) {
-        // ---- activation half-tile: 512 rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist and are zero
+    } else if (warp < 19) {
+        // ---- activation half-tile: 512 rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist and are zero.
+        //      The copies of up to three slots are in flight per thread (one cp.async group per slot).
         const int b = threadIdx.x - kAThreads;
-        for (int q = 0; q < n_slots; ++q) {
-            const int slot = q % kTSlots;
-            if (!bar_wait(s32(&s_empty[slot]), ((q / kTSlots) & 1) ^ 1, failed)) break;
+        int issued = 0;
+        bool alive = true;
+        auto issue = [&]() {  // copies of slot `issued`, once the MMAs that read its previous contents are done
+            const int slot = issued % kTSlots;
+            if (!bar_wait(s32(&s_empty[slot]), ((issued / kTSlots) & 1) ^ 1, failed)) {
+                alive = false;
+                return;
+            }
             const uint32_t b_tile = tiles + (slot >> 1) * kTStage + kTA;
-            const __half *src = xh + static_cast<size_t>(tok0) * cols + (q >> 1) * kTK + (slot & 1) * 32;
+            const __half *src = xh + static_cast<size_t>(tok0) * cols + (issued >> 1) * kTK + (slot & 1) * 32;
             for (int i = b; i < kTN * 4; i += kBThreads) {
                 const int n = i >> 2, c = (slot & 1) * 4 + (i & 3);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_tile + n * 128 + ((c ^ (n & 7)) << 4)),
@@ -175,10 +187,20 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
                              : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            ++issued;
+        };
+        while (alive && issued < n_slots && issued < 3) issue();
+        for (int q = 0; alive && q < n_slots; ++q) {
+            // groups complete in order: slot q has landed once at most (issued - q - 1) groups are still pending
+            const int pending = issued - q - 1;
+            if (pending >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            bar_arrive(s32(&s_full[slot]));
+            bar_arrive(s32(&s_full[q % kTSlots]));
+            if (issued < n_slots) issue();
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (lane == 0) {
         // ---- MMA issue: accumulator 0 (activation rows 0..255) at column 0, accumulator 1 at column 256
         for (int q = 0; q < n_slots; ++q) {
