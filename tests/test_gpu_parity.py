@@ -497,3 +497,19 @@ def test_prompt_gemm_tcgen05_matches_the_matvec_path_for_every_type(rt, codebook
     assert np.all(np.abs(got - ref) <= 3e-3 * np.abs(ref).max())
     oracle = O.matvec(raw, int(t), rows, cols, x, codebooks)
     assert rel_l2(got, oracle) <= 2e-3  # fp16 rounding of both operands
+
+
+@pytest.mark.parametrize("t,rows,cols,ntok", [
+    (T.Q6_K, 12288, 5120, 4), (T.Q5_K, 10240, 5120, 1), (T.Q8_0, 6144, 5120, 8), (T.Q8_0, 48, 5120, 4), (T.F32, 48, 5120, 3),
+    (T.Q5_K, 5120, 6144, 4), (T.F16, 256, 5120, 2), (T.Q6_K, 19000, 5120, 5), (T.Q4_K, 641, 17408, 7),
+], ids=lambda v: getattr(v, "name", str(v)))
+def test_qmv_real_model_shapes(rt, clib, codebooks, t, rows, cols, ntok):
+    """Shapes of the real 27B tensor set that the synthetic layer set leaves out (engine/src/vinf/gguf/qwen_tensors.py:108-118):
+    the gated 12288-row q, the SSM projections of 10240 / 6144 / 48 rows with their Q5_K / Q8_0 / F32 types, an LM-head
+    shard, and an odd-sized shard of the down projection."""
+    rng = np.random.default_rng(rows + cols + ntok)
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    got = run_qmv(rt, raw, t, rows, cols, x)
+    ref = oracle_libs.c_qmv(clib, raw, int(t), rows, cols, x, codebooks)
+    assert rel_l2(got, ref) <= REL_L2
