@@ -1,4 +1,4 @@
-// Tuned step decoders for Q4_K, Q6_K and Q3_K (the types of the 27B layer set).  See vqm_steps.cuh for the interface.
+// Tuned step decoders for Q4_K, Q5_K, Q6_K and Q3_K (the types of the 27B layer set).  See vqm_steps.cuh for the interface.
 //
 // Common idea: the per-weight work is "raw field -> float" (one byte permute: the field becomes the subnormal
 // field * 2^-141, see bytes_to_subpair), one packed multiply or FMA per two weights with the group scale dl * 2^64
@@ -24,8 +24,15 @@ namespace vqm {
 //   dot pass   : one block at a time, lane i -> 32-bit word i of the nibbles: 4 weights of group 2p (columns
 //                64p + 4(i%8) ..) and 4 of group 2p+1 (32 columns further), p = i / 8.  Eight lanes read 128
 //                contiguous bytes of activations per load, so the shared-memory reads are conflict-free.
-template <int M, int RW>
-struct Step<kQ4_K, M, RW> {
+// Q5_K (176 B, 16-byte aligned) is the same with a fifth bit: d, dmin | 12 bytes of scales and mins | 32 bytes of high
+// bits (bit g of byte l belongs to weight 32g + l) | 128 bytes of nibbles (engine/csrc/common/qwen_quant.cuh:176-181).
+// The lane that owns nibble word i also reads high-bit word i % 8; the high nibbles are shifted down so that the
+// fifth bit fits into the byte.
+template <int TYPE, int M, int RW>
+struct K45Step {
+    static_assert(TYPE == kQ4_K || TYPE == kQ5_K, "Q4_K or Q5_K");
+    static constexpr bool kFive = TYPE == kQ5_K;
+    static constexpr int kBlock = kFive ? 176 : 144, kNibbles = kFive ? 48 : 16;
     // piece 2w: scales, piece 2w + 1: mins of pair p = 2hh + w; slot (row * 4 + block) * 2 + hh of 16 bytes in each piece
     static constexpr int kPiece = RW * 4 * 2 * 16 + 32;  // + 32: consecutive pieces start 8 banks apart
     static constexpr int kScratch = 4 * kPiece;
@@ -33,9 +40,9 @@ struct Step<kQ4_K, M, RW> {
 
     template <int NR>
     struct Pass {
-        // One block of every row: lane i -> nibble word i.
-        static __device__ __forceinline__ void block_dot(uint32_t wl, uint32_t el, uint32_t xl, f32x2 (&acc)[RW][M]) {
-            constexpr int SLOT = slot_bytes(kQ4_K);
+        // One block of every row: lane i -> nibble word i (p = i / 8: groups 2p and 2p + 1).
+        static __device__ __forceinline__ void block_dot(uint32_t wl, uint32_t hl, int p, uint32_t el, uint32_t xl, f32x2 (&acc)[RW][M]) {
+            constexpr int SLOT = slot_bytes(TYPE);
             X4 xa[M], xb[M];
             f32x2 sx[M];
 #pragma unroll
@@ -47,10 +54,18 @@ struct Step<kQ4_K, M, RW> {
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 const uint32_t w = lds32(wl + r * SLOT);
-                const uint32_t lo = w & 0x0F0F0F0Fu, hi = w & 0xF0F0F0F0u;
-                const ulonglong2 dl = lds128(el + r * 128);           // (dl, dl), (dl'/16, dl'/16), each times 2^64
+                uint32_t lo, hi;
+                if constexpr (kFive) {
+                    const uint32_t qh = lds32(hl + r * SLOT) >> (2 * p);
+                    lo = (w & 0x0F0F0F0Fu) | ((qh << 4) & 0x10101010u);
+                    hi = ((w >> 4) & 0x0F0F0F0Fu) | ((qh << 3) & 0x10101010u);
+                } else {
+                    lo = w & 0x0F0F0F0Fu;
+                    hi = w & 0xF0F0F0F0u;  // 16 x the field; the scale table carries dl' / 16
+                }
+                const ulonglong2 dl = lds128(el + r * 128);           // (dl, dl), (dl', dl') [Q4_K: dl' / 16], each times 2^64
                 const f32x2 nml = lds64(el + r * 128 + kPiece);      // (-ml, -ml') times 2^-77
-                // exact products (at most 21 significant bits): the dequantised weights without their minimum, times 2^-77
+                // exact products (at most 22 significant bits): the dequantised weights without their minimum, times 2^-77
                 const f32x2 a01 = mul2(bytes_to_subpair<0, 1>(lo), dl.x), a23 = mul2(bytes_to_subpair<2, 3>(lo), dl.x);
                 const f32x2 b01 = mul2(bytes_to_subpair<0, 1>(hi), dl.y), b23 = mul2(bytes_to_subpair<2, 3>(hi), dl.y);
 #pragma unroll
@@ -61,19 +76,20 @@ struct Step<kQ4_K, M, RW> {
         }
 
         static __device__ __forceinline__ void go(uint32_t stage, uint32_t scratch, uint32_t xs, int nblk, f32x2 (&acc)[RW][M], int lane) {
-            constexpr int SLOT = slot_bytes(kQ4_K);
+            constexpr int SLOT = slot_bytes(TYPE);
             const f32x2 neg_magic = pack2(-8388608.0f, -8388608.0f);
             // ---- scale pass
 #pragma unroll
             for (int r0 = 0; r0 < NR; r0 += 4) {
                 const int r = r0 + (lane >> 3), blk = (lane >> 1) & 3, hh = lane & 1;
                 if (r < NR) {
-                    const uint4 h = lds128u(stage + r * SLOT + blk * 144);
+                    const uint4 h = lds128u(stage + r * SLOT + blk * kBlock);
                     const float d = half_bits_to_float(h.x & 0xFFFFu) * kSubScale, ndmin = -half_bits_to_float(h.x >> 16) * kSubWeight;
                     // four 6-bit fields at a time (engine/csrc/common/qwen_quant.cuh:78-86)
                     const uint32_t scw = hh ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
                     const uint32_t mnw = hh ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
-                    const f32x2 dlo = pack2(d, d), dhi = pack2(d * 0.0625f, d * 0.0625f), mm = pack2(ndmin, ndmin);
+                    const float dh = kFive ? d : d * 0.0625f;
+                    const f32x2 dlo = pack2(d, d), dhi = pack2(dh, dh), mm = pack2(ndmin, ndmin);
                     const uint32_t dst = scratch + ((r * 4 + blk) * 2 + hh) * 16;
                     sts128(dst, mul2(bytes_to_pair<0, 0>(scw, neg_magic), dlo), mul2(bytes_to_pair<1, 1>(scw, neg_magic), dhi));
                     sts128(dst + kPiece, mul2(bytes_to_pair<0, 1>(mnw, neg_magic), mm), 0ull);
@@ -86,13 +102,13 @@ struct Step<kQ4_K, M, RW> {
             const int p = lane >> 3;
             const uint32_t xl = xs + (p * 64 + 4 * (lane & 7)) * 4;
             const uint32_t el = scratch + (p & 1) * 2 * kPiece + (p >> 1) * 16;
-            const uint32_t wl = stage + 16 + 4 * lane;
+            const uint32_t wl = stage + kNibbles + 4 * lane, hl = stage + 16 + 4 * (lane & 7);
             if (nblk == 4) {  // a full segment: straight-line code
 #pragma unroll
-                for (int blk = 0; blk < 4; ++blk) block_dot(wl + blk * 144, el + blk * 32, xl + blk * 1024, acc);
+                for (int blk = 0; blk < 4; ++blk) block_dot(wl + blk * kBlock, hl + blk * kBlock, p, el + blk * 32, xl + blk * 1024, acc);
             } else {
 #pragma unroll 1
-                for (int blk = 0; blk < nblk; ++blk) block_dot(wl + blk * 144, el + blk * 32, xl + blk * 1024, acc);
+                for (int blk = 0; blk < nblk; ++blk) block_dot(wl + blk * kBlock, hl + blk * kBlock, p, el + blk * 32, xl + blk * 1024, acc);
             }
             __syncwarp();  // the scratch table is rewritten by the next step
         }
@@ -103,6 +119,11 @@ struct Step<kQ4_K, M, RW> {
         dispatch_rows<Pass, RW>(nrows, stage, scratch, xs, cols >> 8, acc, lane);
     }
 };
+
+template <int M, int RW>
+struct Step<kQ4_K, M, RW> : K45Step<kQ4_K, M, RW> {};
+template <int M, int RW>
+struct Step<kQ5_K, M, RW> : K45Step<kQ5_K, M, RW> {};
 
 // ---- Q6_K and Q3_K ---------------------------------------------------------------------------------------------
 // Both share a block geometry: weight e = 128h + 32q + l (h: half, q: quarter, l < 32) takes its low bits from byte
@@ -189,7 +210,9 @@ struct QuarterFormat<kQ3_K> {
 template <int TYPE, int M, int RW>
 struct QuarterStep {
     using F = QuarterFormat<TYPE>;
-    static constexpr int kEntry = 128;  // per (row, block): 16 sub-scales x (dl, dl), as [h][l >> 4][quarter]
+    // per (row, block): 16 sub-scales x (dl, dl), as [h][l >> 4][quarter], 128 bytes + 16 of padding: the two blocks whose
+    // lanes share a 64-bit load phase then read different banks
+    static constexpr int kEntry = 144;
     static constexpr int kScratch = RW * 4 * kEntry;
     static constexpr float kOutScale = kSubOutScale;
 
