@@ -165,6 +165,47 @@ def cpu_baseline(m: int, seconds: float) -> dict:
             "sample": f"{arm.sample}; best of {len(times)} passes in ~{seconds:.0f} s"}
 
 
+def reference_cuda_kernel(m: int) -> dict | None:
+    """Part of the baseline leg: the reference's own CUDA matvec kernel (its qwen_runtime.cu compiled unchanged for
+    sm_100a into oracle/_ref) timed on this GPU on the tensor of the roofline leg, Q3_K 17408 x 5120, over 4 copies
+    (153 MB, larger than L2).  None if that module has not been built."""
+    import importlib.util
+
+    import torch
+
+    path = REPO / "oracle" / "_ref" / "_cuda_qwen_runtime.so"
+    if not path.exists():
+        return None
+    spec = importlib.util.spec_from_file_location("_cuda_qwen_runtime", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
+        ref = mod.Runtime(z["iq3s_grid"].tobytes())
+    rows, cols, copies = 17408, 5120, 4
+    rng = np.random.default_rng(0)
+    raw = synthetic_blocks(T.Q3_K, rows, cols, rng).tobytes()
+    for i in range(copies):
+        ref.upload(f"w{i}", raw, int(T.Q3_K), cols, rows)
+    ref.alloc("x", m * cols)
+    ref.alloc("y", m * rows)
+    ref.write("x", synthetic_activations(m, cols, rng).tobytes())
+    stream = torch.cuda.default_stream()  # the reference launches on the legacy default stream
+    best = float("inf")
+    for rep in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(copies):
+            ref.qmv(f"w{i}", "x", "y", m)
+        e1.record(stream)
+        ref.synchronize()
+        if rep:
+            best = min(best, e0.elapsed_time(e1) / copies)
+    for i in range(copies):
+        ref.free(f"w{i}")
+    return {"kernel": "reference vinf_qmatvec_kernel rebuilt for sm_100a, Q3_K 17408x5120", "us_per_launch": best * 1e3,
+            "weight_GBs": len(raw) / (best * 1e-3) / 1e9}
+
+
 def run_reference(args) -> None:
     """--impl reference: the reference's CPU implementation of the path on this host's cores.  Rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -472,6 +513,10 @@ def run_gpu(args) -> None:
             "clocks": clocks,
         }
         if cpu is not None:
+            ref_kernel = reference_cuda_kernel(m)
+            if ref_kernel is not None:
+                ref_kernel["this_kernel_speedup"] = ref_kernel["us_per_launch"] / (dom_ms * 1e3)
+                cpu["reference_cuda_kernel"] = ref_kernel
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
     torch.cuda.synchronize()

@@ -72,3 +72,14 @@ def load_reference_cpu_module():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
+
+
+def load_reference_cuda_module():
+    """The reference's own CUDA runtime rebuilt for sm_100a, if `make -C oracle ref` has built it; else None."""
+    found = ORACLE / "_ref" / "_cuda_qwen_runtime.so"
+    if not found.exists():
+        return None
+    spec = importlib.util.spec_from_file_location("_cuda_qwen_runtime", found)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
