@@ -397,7 +397,16 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                         sums[r * M + t] = lo + hi;
                         acc[r][t] = 0ull;
                     }
-                float mine = warp_sums(sums, lane);
+                float mine = 0.0f;
+                if constexpr (RW * M > 16) {
+                    mine = warp_sums(sums, lane);  // (measured: pays above 16 sums; below, its selects cost registers)
+                } else {
+#pragma unroll
+                    for (int i = 0; i < RW * M; ++i) {
+                        const float s = warp_sum(sums[i]);
+                        if (lane == i) mine = s;
+                    }
+                }
                 if (lane < RW * M) {
                     const int r = lane / M, t = lane % M, row = row0 + r;
                     if (r < nrows) {
