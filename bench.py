@@ -39,7 +39,7 @@ from vinf_3080ti_b200.synth import LAYER_SET, LM_HEAD, N_LAYERS, synthetic_activ
 
 METRIC = "quant-matvec weight GB/s, synthetic-27B decode pass"
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture (profiles/qmv_Q3_K_17408x5120_M4.md)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 38448640
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 38447616
 
 
 # ---- helpers ---------------------------------------------------------------------------------------------
