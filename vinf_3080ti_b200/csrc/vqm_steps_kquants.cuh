@@ -219,15 +219,17 @@ struct QuarterStep {
     template <int NR>
     struct Pass {
         // Four of the lane's columns (xa: their activations) of one quarter, every row.
-        static __device__ __forceinline__ void quad_dot(const uint32_t (&q)[NR], const f32x2 (&d2)[NR], const f32x2 (&c2)[NR], uint32_t xa,
-                                                        f32x2 (&acc)[RW][M]) {
+        static __device__ __forceinline__ void quad_dot(const uint32_t (&q)[NR], const f32x2 (&d2)[NR], uint32_t xa, f32x2 (&acc)[RW][M]) {
+            const f32x2 nbias = pack2(-F::kBias * 0x1p-141f, -F::kBias * 0x1p-141f);
             X4 x[M];
 #pragma unroll
             for (int t = 0; t < M; ++t) x[t] = lds_x4(xa + t * kSegCols * 4);
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 // exact: field * 2^-141 * dl * 2^64 - bias * dl * 2^-77, the dequantised weight times 2^-77
-                const f32x2 q01 = fma2(bytes_to_subpair<0, 1>(q[r]), d2[r], c2[r]), q23 = fma2(bytes_to_subpair<2, 3>(q[r]), d2[r], c2[r]);
+                // (c is recomputed per four columns rather than kept per row: a multiply is cheaper than the registers)
+                const f32x2 c = mul2(d2[r], nbias);
+                const f32x2 q01 = fma2(bytes_to_subpair<0, 1>(q[r]), d2[r], c), q23 = fma2(bytes_to_subpair<2, 3>(q[r]), d2[r], c);
 #pragma unroll
                 for (int t = 0; t < M; ++t) acc[r][t] = fma2(q23, x[t].p23, fma2(q01, x[t].p01, acc[r][t]));
             }
@@ -236,19 +238,17 @@ struct QuarterStep {
         template <int Q>
         static __device__ __forceinline__ void quarter_dot(const typename F::Words (&first)[NR], const typename F::Words (&second)[NR],
                                                            uint32_t el, uint32_t x_first, uint32_t x_second, f32x2 (&acc)[RW][M]) {
-            const f32x2 nbias = pack2(-F::kBias * 0x1p-141f, -F::kBias * 0x1p-141f);
             uint32_t q[NR];
-            f32x2 d2[NR], c2[NR];
+            f32x2 d2[NR];
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 d2[r] = lds64(el + r * 4 * kEntry + Q * 8);
-                c2[r] = mul2(d2[r], nbias);
                 q[r] = F::template quarter<Q>(first[r]);
             }
-            quad_dot(q, d2, c2, x_first + Q * 32 * 4, acc);
+            quad_dot(q, d2, x_first + Q * 32 * 4, acc);
 #pragma unroll
             for (int r = 0; r < NR; ++r) q[r] = F::template quarter<Q>(second[r]);
-            quad_dot(q, d2, c2, x_second + Q * 32 * 4, acc);
+            quad_dot(q, d2, x_second + Q * 32 * 4, acc);
         }
 
         static __device__ __forceinline__ void go(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t scratch, uint32_t xs, int nblk,
