@@ -19,6 +19,15 @@
 //     with packed fp32 FMAs, then a warp xor-shuffle tree.  The order of additions for an output does not
 //     depend on M or RW, so an M-row pass equals M single-row passes bit for bit, as the reference
 //     guarantees (engine/csrc/megakernel/qwen_runtime.cu:575-577).
+//   * One launch can cover up to four tensors that share x, the type and the columns (q/k/v, gate/up): the launch
+//     numbers their rows consecutively and a chain of selects maps a row to its tensor's weights and outputs.
+//   * Short launches (the rows would leave more than half of the warps idle) are split by columns: the blocks of a
+//     thread-block cluster share a group of rows, one row per warp, and a share of the columns each; partial sums go
+//     to the first block's shared memory (distributed shared memory), one cluster barrier, and that block adds them in
+//     column order.  The split depends on the rows and columns only, never on M.
+//   * Row-sharded launches (several GPUs) store every output into the gathered vector inside each rank's exchange
+//     region as well (plain remote stores) and the last block to finish raises this rank's flag in every region; a
+//     consumer launch waits, bounded, for the flags of its producer.
 //   * Optional fused argmax over the rows (the LM head): every warp keeps the best (value, row) per
 //     activation row, blocks write partials, the last block to finish reduces them.  Ties go to the
 //     lowest row and a column with no value above -inf yields 0x7fffffff, like the reference's
