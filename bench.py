@@ -513,7 +513,11 @@ def run_gpu(args) -> None:
             "clocks": clocks,
         }
         if cpu is not None:
-            ref_kernel = reference_cuda_kernel(m)
+            try:
+                ref_kernel = reference_cuda_kernel(m)
+            except Exception as exc:  # the baseline leg must never take the measurement down with it
+                ref_kernel = None
+                cpu["reference_cuda_kernel_error"] = f"{type(exc).__name__}: {exc}"[:200]
             if ref_kernel is not None:
                 ref_kernel["this_kernel_speedup"] = ref_kernel["us_per_launch"] / (dom_ms * 1e3)
                 cpu["reference_cuda_kernel"] = ref_kernel
