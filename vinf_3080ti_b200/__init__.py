@@ -4,11 +4,11 @@ sharding across GPUs.  See runtime.Runtime for the drop-in interface and include
 """
 from .gguf_types import CUDA_MATVEC_TYPES, GGUFTensorType, TRAITS, row_bytes  # noqa: F401
 
-__all__ = ["CUDA_MATVEC_TYPES", "GGUFTensorType", "TRAITS", "row_bytes", "Runtime", "CudaWeightRuntime"]
+__all__ = ["CUDA_MATVEC_TYPES", "GGUFTensorType", "TRAITS", "row_bytes", "Runtime"]
 
 
 def __getattr__(name):  # the runtime needs the built library; the type tables do not
-    if name in ("Runtime", "CudaWeightRuntime"):
+    if name == "Runtime":
         from . import runtime
 
         return getattr(runtime, name)

@@ -45,13 +45,8 @@ namespace vqm {
 
 constexpr int kWarps = 8;                      // warps per block
 constexpr int kMaxTok = 8;                     // activation rows per launch
-constexpr int kWarpSmemBudget = 5120;          // weight staging bytes a warp aims for (at least two stages are kept)
 constexpr int kBarrierBytes = 1024;            // mbarriers and counters at the front of shared memory
 
-__host__ __device__ constexpr int stages_for(int type, int rw) {
-    const int s = kWarpSmemBudget / (rw * slot_bytes(type));
-    return s < 2 ? 2 : s > 8 ? 8 : s;
-}
 __host__ __device__ constexpr int table_bytes_padded(int type) { return (grid_bytes(type) + 15) / 16 * 16; }
 
 // Blocks per SM the register allocation aims for: two, except for the tall chunks of wide passes (their sums alone
@@ -59,21 +54,31 @@ __host__ __device__ constexpr int table_bytes_padded(int type) { return (grid_by
 #ifndef VQM_MIN_BLOCKS
 #define VQM_MIN_BLOCKS(M, RW) (((M) <= 4 || (RW) == 1) ? 2 : 1)
 #endif
+#ifndef VQM_MAX_STAGES
+#define VQM_MAX_STAGES 4
+#endif
+#ifndef VQM_X_STAGES
+#define VQM_X_STAGES 2
+#endif
 
-// Activation stages: as many (2..4) as leave room for the blocks per SM the kernel aims for (228 KB of shared memory per
-// SM, 1 KB of it reserved per block).
+// Shared memory goes to the HBM stream first: two activation stages (the activations are small and sit in L2), then as
+// many weight stages per warp (2..VQM_MAX_STAGES) as fit beside them when the kernel's blocks share an SM
+// (228 KB per SM, 1 KB of it reserved per block, ~5 KB of static arrays per block).
 template <int TYPE, int M, int RW>
 __host__ __device__ constexpr int x_stages() {
-    constexpr int fixed = table_bytes_padded(TYPE) + kBarrierBytes + kWarps * stages_for(TYPE, RW) * RW * slot_bytes(TYPE) +
-                          kWarps * Step<TYPE, M, RW>::kScratch;
-    constexpr int budget = (VQM_MIN_BLOCKS(M, RW) >= 2 ? 108 : 200) * 1024;  // dynamic part; the kernel has ~5 KB of static arrays
-    constexpr int s = (budget - fixed) / (M * kSegCols * 4);
-    return s < 2 ? 2 : s > 4 ? 4 : s;
+    return VQM_X_STAGES;
+}
+template <int TYPE, int M, int RW>
+__host__ __device__ constexpr int w_stages() {
+    constexpr int fixed = table_bytes_padded(TYPE) + kBarrierBytes + x_stages<TYPE, M, RW>() * M * kSegCols * 4 + kWarps * Step<TYPE, M, RW>::kScratch;
+    constexpr int budget = (VQM_MIN_BLOCKS(M, RW) >= 2 ? 108 : 200) * 1024;
+    constexpr int s = (budget - fixed) / (kWarps * RW * slot_bytes(TYPE));
+    return s < 2 ? 2 : s > VQM_MAX_STAGES ? VQM_MAX_STAGES : s;
 }
 template <int TYPE, int RW, int M>
 __host__ __device__ constexpr size_t matvec_smem_bytes_for() {
     return static_cast<size_t>(table_bytes_padded(TYPE)) + kBarrierBytes + static_cast<size_t>(x_stages<TYPE, M, RW>()) * M * kSegCols * 4 +
-           static_cast<size_t>(kWarps) * stages_for(TYPE, RW) * RW * slot_bytes(TYPE) + static_cast<size_t>(kWarps) * Step<TYPE, M, RW>::kScratch;
+           static_cast<size_t>(kWarps) * w_stages<TYPE, M, RW>() * RW * slot_bytes(TYPE) + static_cast<size_t>(kWarps) * Step<TYPE, M, RW>::kScratch;
 }
 
 // ---- mbarrier / bulk-copy primitives ---------------------------------------------------------------
@@ -191,7 +196,7 @@ __device__ __forceinline__ uintptr_t row_address(const MatvecArgs &a, int g) {
 template <int TYPE, int M, int RW>
 __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel(const MatvecArgs a) {
     using StepT = Step<TYPE, M, RW>;
-    constexpr int S = stages_for(TYPE, RW);
+    constexpr int S = w_stages<TYPE, M, RW>();
     constexpr int XS = x_stages<TYPE, M, RW>();
     constexpr int SLOT = slot_bytes(TYPE);
     constexpr int SEG = seg_bytes(TYPE);

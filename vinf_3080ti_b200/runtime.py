@@ -3,7 +3,8 @@
 `Runtime` has the method names, argument orders, defaults and exception types of the reference's CPython
 type `vinf._cuda_qwen_runtime.Runtime` (engine/csrc/megakernel/qwen_runtime.cu:2602-2704) for everything on
 the matvec path, so an executor that is handed one as its `runtime=` (engine/src/vinf/qwen_gpu.py:227,253-259)
-calls it unchanged.  `CudaWeightRuntime` mirrors the thin wrapper engine/src/vinf/cuda/qwen_runtime.py:47-116.
+calls it unchanged.  The reference's thin Python wrapper (engine/src/vinf/cuda/qwen_runtime.py:47-116) keeps working
+on top of it: it only forwards to whatever module object its loader returns.
 
 All work is done by libvinf_b200.so through its C ABI; this file only converts arguments and errors.
 Weights are always resident in HBM, so the reference's host-staging / VMM-group methods are kept as
@@ -12,14 +13,12 @@ no-ops with trivial answers.
 from __future__ import annotations
 
 import ctypes
-import struct
-from array import array
 from typing import Sequence
 
 import numpy as np
 
 from . import _capi
-from .gguf_types import CODEBOOK_BYTES, CUDA_MATVEC_TYPES, GGUFTensorType
+from .gguf_types import CODEBOOK_BYTES
 
 MAX_ARGMAX_ROWS = 256  # engine/csrc/megakernel/qwen_runtime.cu:573
 
@@ -378,67 +377,3 @@ class Runtime:
 
     def vmm_granularity(self) -> int:
         return 2 * 1024 * 1024
-
-
-class CudaWeightRuntime:
-    """Persistent HBM store of raw GGUF tensors with quantized matvec
-    (mirror of engine/src/vinf/cuda/qwen_runtime.py:47-116)."""
-
-    def __init__(self, codebooks: dict[str, bytes] | None = None) -> None:
-        books = dict(reference_codebooks())
-        books.update(codebooks or {})
-        self._rt = Runtime(books.get("iq3s_grid"), books)
-
-    def mem_info(self) -> tuple[int, int]:
-        return self._rt.mem_info()
-
-    def device_bytes(self) -> int:
-        return self._rt.device_bytes()
-
-    def has(self, name: str) -> bool:
-        return self._rt.has(name)
-
-    def free(self, name: str) -> None:
-        self._rt.free(name)
-
-    def upload_gguf_tensor(self, gguf, name: str, *, device_name: str | None = None, resident: bool = True,
-                           group: int = -1) -> int:
-        """Uploads a tensor of a parsed GGUF file (an object with the reference's GGUFFile interface:
-        .tensors[name] with tensor_type / dimensions / nbytes, and .mmap_tensor(name))."""
-        tensor = gguf.tensors[name]
-        if int(tensor.tensor_type) not in {int(t) for t in CUDA_MATVEC_TYPES}:
-            raise ValueError(f"{name}: no CUDA matvec for {getattr(tensor.tensor_type, 'name', tensor.tensor_type)}")
-        cols = tensor.dimensions[0]  # GGUF dimension order is fastest-first
-        rows = 1
-        for dim in tensor.dimensions[1:]:
-            rows *= dim
-        file_obj, mm, view = gguf.mmap_tensor(name)
-        try:
-            self._rt.upload(device_name or name, view, int(tensor.tensor_type), cols, rows, resident, group)
-        finally:
-            view.release()
-            mm.close()
-            file_obj.close()
-        return tensor.nbytes
-
-    def upload_raw(self, name: str, data, tensor_type: GGUFTensorType | int, cols: int, rows: int, *,
-                   resident: bool = True) -> None:
-        self._rt.upload(name, data, int(tensor_type), cols, rows, resident)
-
-    def matvec(self, name: str, values: Sequence[float]) -> list[float]:
-        out = array("f")
-        out.frombytes(self._rt.matvec(name, array("f", values).tobytes()))
-        return out.tolist()
-
-    def read_floats(self, name: str, n: int = -1, offset: int = 0) -> list[float]:
-        """Buffer contents as floats (fp16 buffers are widened)."""
-        data = self._rt.read(name, n, offset)
-        if self._rt.buffer_elem(name) == 2:
-            return list(struct.unpack(f"<{len(data) // 2}e", data))
-        out = array("f")
-        out.frombytes(data)
-        return out.tolist()
-
-    def __getattr__(self, name: str):
-        # device-op passthrough (qmv, argmax, argmax_rows, alloc, write, ...)
-        return getattr(self._rt, name)
