@@ -51,8 +51,14 @@ __host__ __device__ constexpr int table_bytes_padded(int type) { return (grid_by
 
 // Blocks per SM the register allocation aims for: two, except for the tall chunks of wide passes (their sums alone
 // take RW * M register pairs).  One-row chunks always get two, which the column split of short launches counts on.
+#ifndef VQM_BLOCKS_SMALL_M
+#define VQM_BLOCKS_SMALL_M 2
+#endif
+#ifndef VQM_BLOCKS_MID_M
+#define VQM_BLOCKS_MID_M 2
+#endif
 #ifndef VQM_MIN_BLOCKS
-#define VQM_MIN_BLOCKS(M, RW) (((M) <= 4 || (RW) == 1) ? 2 : 1)
+#define VQM_MIN_BLOCKS(M, RW) ((RW) == 1 ? 2 : (M) <= 2 ? VQM_BLOCKS_SMALL_M : (M) <= 4 ? VQM_BLOCKS_MID_M : 1)
 #endif
 #ifndef VQM_MAX_STAGES
 #define VQM_MAX_STAGES 4
@@ -71,7 +77,7 @@ __host__ __device__ constexpr int x_stages() {
 template <int TYPE, int M, int RW>
 __host__ __device__ constexpr int w_stages() {
     constexpr int fixed = table_bytes_padded(TYPE) + kBarrierBytes + x_stages<TYPE, M, RW>() * M * kSegCols * 4 + kWarps * Step<TYPE, M, RW>::kScratch;
-    constexpr int budget = (VQM_MIN_BLOCKS(M, RW) >= 2 ? 108 : 200) * 1024;
+    constexpr int budget = (VQM_MIN_BLOCKS(M, RW) >= 3 ? 70 : VQM_MIN_BLOCKS(M, RW) == 2 ? 108 : 200) * 1024;
     constexpr int s = (budget - fixed) / (kWarps * RW * slot_bytes(TYPE));
     return s < 2 ? 2 : s > VQM_MAX_STAGES ? VQM_MAX_STAGES : s;
 }
@@ -94,25 +100,27 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll.  The instruction itself may suspend the thread for up to `hint_ns` nanoseconds while the phase is still open,
+// so a waiting warp issues a handful of instructions instead of spinning.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
 
-// Bounded wait: ~2^22 polls with a short sleep after the first few hundred.
+// Bounded wait: at most 2^18 polls of up to ~20 microseconds each (a few seconds: longer than the bounded wait for another
+// rank's push, which comes first in a kernel and must be the one that reports), then the caller reports the expiry.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity, 2000u)) return true;
 #pragma unroll 1
-    for (int i = 0; i < (1 << 22); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 256) __nanosleep(64);
-    }
+    for (int i = 0; i < (1 << 18); ++i)
+        if (mbar_try_wait(bar, parity, 20000u)) return true;
     return false;
 }
 
@@ -252,16 +260,17 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     const int col_begin = kpart * n_units / k_split * 256;
     const int col_end = (kpart + 1) * n_units / k_split * 256 < a.cols ? (kpart + 1) * n_units / k_split * 256 : a.cols;
     const int n_seg = (col_end - col_begin + kSegCols - 1) / kSegCols;
-    const int n_steps = n_chunks * n_seg;
     constexpr int CB = chunk_block(TYPE), CBB = chunk_block_bytes(TYPE);
     const uint32_t byte_begin = static_cast<uint32_t>(col_begin / CB * CBB), byte_end = static_cast<uint32_t>(col_end / CB * CBB);
+    const int cols_last = col_end - col_begin - (n_seg - 1) * kSegCols;                       // columns of the last segment
+    const uint32_t len_last = byte_end - byte_begin - static_cast<uint32_t>(n_seg - 1) * SEG;  // and its bytes
     const uint32_t w_align = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(a.part[0].w) & 15u);
     const uint32_t rb16 = static_cast<uint32_t>(a.row_bytes) & 15u;
 
-    // Activation stage for step `step` (segment `seg`): one bulk copy per activation row.  Called by one thread.
+    // Activation stage of segment `seg`: one bulk copy per activation row.  Called by one thread.
     auto issue_x = [&](int xstage, int seg) {
         const int col0 = col_begin + seg * kSegCols;
-        const int cols_here = col_end - col0 < kSegCols ? col_end - col0 : kSegCols;
+        const int cols_here = seg == n_seg - 1 ? cols_last : kSegCols;
         mbar_expect_tx(xfull + xstage * 8, static_cast<uint32_t>(M * cols_here * 4));
 #pragma unroll
         for (int t = 0; t < M; ++t)
@@ -269,32 +278,33 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                           static_cast<uint32_t>(cols_here * 4), xfull + xstage * 8);
     };
 
-    // Weight issue side: lane r (< rows of the chunk) walks the byte range of row `i_row0 + r`, one segment per step.
-    int i_chunk = 0, i_row0 = my_begin, i_nrows = chunk_base + (0 < chunk_rem ? 1 : 0), i_seg = 0, i_stage = 0;
-    uintptr_t i_row_at = row_address(a, i_row0 + lane);
-    auto issue_w = [&]() {
-        if (i_nrows > 0) {  // warp-uniform
-            uint32_t bytes = 0;
-            uintptr_t src = 0;
-            if (lane < i_nrows) {
-                const uint32_t off = byte_begin + static_cast<uint32_t>(i_seg) * SEG;
-                const uint32_t len = byte_end - off < SEG ? byte_end - off : SEG;
-                const uintptr_t p = i_row_at + off;
-                src = p & ~static_cast<uintptr_t>(15);
-                bytes = static_cast<uint32_t>((p - src + len + 15) & ~static_cast<uintptr_t>(15));
-            }
-            const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
-            if (lane == 0) mbar_expect_tx(bar + i_stage * 8, total);
+    // Weight issue side, S stages ahead of the consumer: lane r (< rows of the chunk) owns row `i_row0 + r` and walks its
+    // bytes one segment per call; `i_at` is where the lane's next segment starts in global memory.
+    int i_chunk = 0, i_row0 = my_begin, i_nrows = chunk_base + (0 < chunk_rem ? 1 : 0), i_seg = 0;
+    uintptr_t i_at = row_address(a, i_row0 + (lane < RW ? lane : 0)) + byte_begin;
+    auto issue_w = [&](uint32_t stage_at, uint32_t i_bar) {  // the stage to fill and its barrier
+        const uint32_t i_slot = stage_at + lane * SLOT;
+        const uint32_t len = i_seg == n_seg - 1 ? len_last : static_cast<uint32_t>(SEG);
+        if constexpr (kAligned) {
+            if (lane == 0) mbar_expect_tx(i_bar, static_cast<uint32_t>(i_nrows) * len);
             __syncwarp();
-            if (bytes) bulk_copy_g2s(buf + (i_stage * RW + lane) * SLOT, reinterpret_cast<const void *>(src), bytes, bar + i_stage * 8);
-            if (++i_stage == S) i_stage = 0;
+            if (lane < i_nrows) bulk_copy_g2s(i_slot, reinterpret_cast<const void *>(i_at), len, i_bar);
+        } else {
+            // the copy is widened to 16-byte boundaries and keeps the segment's offset inside its 16-byte line
+            const uint32_t lead = static_cast<uint32_t>(i_at) & 15u;
+            const uint32_t bytes = lane < i_nrows ? (lead + len + 15u) & ~15u : 0u;
+            const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+            if (lane == 0) mbar_expect_tx(i_bar, total);
+            __syncwarp();
+            if (bytes) bulk_copy_g2s(i_slot, reinterpret_cast<const void *>(i_at - lead), bytes, i_bar);
         }
+        i_at += SEG;
         if (++i_seg == n_seg) {
             i_seg = 0;
             i_row0 += i_nrows;
             ++i_chunk;
             i_nrows = chunk_base + (i_chunk < chunk_rem ? 1 : 0);
-            i_row_at = row_address(a, i_row0 + lane);
+            i_at = row_address(a, i_row0 + (lane < RW ? lane : 0)) + byte_begin;
         }
     };
 
@@ -303,8 +313,11 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     // may have started while the previous kernel of the stream was still draining, which hides the launch latency
     // and the first-byte latency of the weight stream (without that launch attribute both instructions are no-ops).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    int issued = 0;
-    for (; issued < S && issued < n_steps; ++issued) issue_w();
+    // (chunks that hold rows come first: once a chunk without rows is reached, or the last chunk is passed, nothing is left)
+#ifndef VQM_PURE_COMPUTE  // (experiment switch: no copies and no waits, the decoders run on whatever shared memory holds)
+#pragma unroll 1
+    for (int s = 0; s < S && i_chunk < n_chunks && i_nrows > 0; ++s) issue_w(buf + s * (RW * SLOT), bar + s * 8);
+#endif
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (warp == 0 && a.push.wait_slot > 0) {
         // Row-sharded input: x was assembled by pushes from every rank.  Lane p waits (bounded) until rank p has pushed
@@ -336,10 +349,13 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
         }
         __syncwarp();
     }
+    const int n_steps = n_chunks * n_seg;  // activation stages every warp of the block walks through
+#ifndef VQM_PURE_COMPUTE
     if (threadIdx.x == 0) {
         const int n = n_steps < XS ? n_steps : XS;
         for (int s = 0; s < n; ++s) issue_x(s, s % n_seg);
     }
+#endif
 
     if constexpr (TABLE > 0) {
         if constexpr (grid_is_codebook(TYPE)) {
@@ -361,111 +377,124 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     const bool want_argmax = a.out_idx != nullptr;
     bool expired = false;
 
-    int stage = 0, xstage = 0, seg = 0, chunk = 0, row0 = my_begin, nrows = chunk_base + (0 < chunk_rem ? 1 : 0);
-    uint32_t phase = 0, xphase = 0;
-    for (int step = 0; step < n_steps; ++step) {
-        if (!mbar_wait_bounded(xfull + xstage * 8, xphase)) {
-            expired = true;
-            break;
-        }
-        const bool active = nrows > 0;
-        if (active) {
-            if (!mbar_wait_bounded(bar + stage * 8, phase)) {
+    uint32_t c_stage = buf, c_bar = bar, phase = 0;  // the weight stage the consumer is at
+    int xstage = 0;
+    uint32_t xphase = 0;
+    int row0 = my_begin;
+    for (int chunk = 0; chunk < n_chunks && !expired; ++chunk) {
+        const int nrows = chunk_base + (chunk < chunk_rem ? 1 : 0);  // warp-uniform; chunks without rows come last
+        // d0: where row 0's segment starts inside its slot (the copy began at the 16-byte boundary below it)
+        uint32_t d0 = kAligned ? 0u : (w_align + static_cast<uint32_t>(row0) * rb16 + byte_begin) & 15u;
+        for (int seg = 0; seg < n_seg; ++seg) {
+#ifndef VQM_PURE_COMPUTE
+            if (!mbar_wait_bounded(xfull + xstage * 8, xphase)) {
                 expired = true;
                 break;
             }
-            // d0: where row 0's segment starts inside its slot (the copy began at the 16-byte boundary below it)
-            const uint32_t d0 = kAligned ? 0u : (w_align + static_cast<uint32_t>(row0) * rb16 + byte_begin + static_cast<uint32_t>(seg) * SEG) & 15u;
-            const int col0 = col_begin + seg * kSegCols;
-            const int cols_here = col_end - col0 < kSegCols ? col_end - col0 : kSegCols;
-            StepT::run(buf + stage * RW * SLOT, d0, kAligned ? 0u : rb16, scratch, smem0, xbuf + xstage * XSTAGE, cols_here, nrows, acc, lane);
-        }
-        __syncwarp();
-        // Done with the activation stage; the last warp of the block to get here refills it.
-        if (lane == 0) {
-            __threadfence_block();
-            if (atomicAdd(xdone + xstage, 1) == kWarps - 1) {
-                xdone[xstage] = 0;
+#endif
+            if (nrows > 0) {
+#ifndef VQM_PURE_COMPUTE
+                if (!mbar_wait_bounded(c_bar, phase)) {
+                    expired = true;
+                    break;
+                }
+#endif
+#ifndef VQM_ABLATE_STEP
+                StepT::run(c_stage, d0, kAligned ? 0u : rb16, scratch, smem0, xbuf + xstage * XSTAGE, seg == n_seg - 1 ? cols_last : kSegCols, nrows,
+                           acc, lane);
+#endif
+            }
+            __syncwarp();
+            // Done with the activation stage; the last warp of the block to get here refills it.
+#ifndef VQM_PURE_COMPUTE
+            if (lane == 0) {
                 __threadfence_block();
-                if (step + XS < n_steps) {
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    issue_x(xstage, (seg + XS) % n_seg);
+                if (atomicAdd(xdone + xstage, 1) == kWarps - 1) {
+                    xdone[xstage] = 0;
+                    __threadfence_block();
+                    if (chunk * n_seg + seg + XS < n_steps) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        issue_x(xstage, (seg + XS) % n_seg);
+                    }
                 }
             }
-        }
-        if (issued < n_steps) {
-            issue_w();
-            ++issued;
-        }
-
-        if (seg == n_seg - 1) {
-            if (active) {
-                // lane r*M + t ends up holding y[t][row0 + r]
-                float sums[RW * M];
-#pragma unroll
-                for (int r = 0; r < RW; ++r)
-#pragma unroll
-                    for (int t = 0; t < M; ++t) {
-                        float lo, hi;
-                        unpack2(acc[r][t], lo, hi);
-                        sums[r * M + t] = lo + hi;
-                        acc[r][t] = 0ull;
-                    }
-                float mine = 0.0f;
-                if constexpr (RW * M > 16) {
-                    mine = warp_sums(sums, lane);  // (measured: pays above 16 sums; below, its selects cost registers)
-                } else {
-#pragma unroll
-                    for (int i = 0; i < RW * M; ++i) {
-                        const float s = warp_sum(sums[i]);
-                        if (lane == i) mine = s;
-                    }
+#endif
+            if (++xstage == XS) {
+                xstage = 0;
+                xphase ^= 1u;
+            }
+            if (nrows > 0) {
+#ifndef VQM_PURE_COMPUTE
+                if (i_chunk < n_chunks && i_nrows > 0) issue_w(c_stage, c_bar);  // refill the stage just consumed
+#endif
+                c_stage += RW * SLOT;
+                c_bar += 8;
+                if (c_bar == bar + S * 8) {
+                    c_bar = bar;
+                    c_stage = buf;
+                    phase ^= 1u;
                 }
-                if (lane < RW * M) {
-                    const int r = lane / M, t = lane % M, row = row0 + r;
-                    if (r < nrows) {
-                        if (k_split > 1) {
-                            // this block's share of the columns only: it goes into the shared memory of the cluster's first
-                            // block, which adds the shares up (one-row chunks: r = 0, lane = t)
-                            uint32_t remote;
-                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&s_split[kpart][warp][t])), "r"(0));
-                            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(mine) : "memory");
-                        } else {
-                            mine *= StepT::kOutScale;  // exact: 1 or a power of two (see bytes_to_subpair)
-                            const RowHome h = home_of(a, row);
-                            if (h.y != nullptr) h.y[static_cast<size_t>(t) * h.rows + h.local] = mine;
-                            if (a.push.push_slot > 0) {
-                                // row-sharded: the value also goes straight into every rank's gathered [M][rows_total] vector
-                                const size_t at = static_cast<size_t>(t) * h.rows_total + h.row_begin + h.local;
-                                for (int p = 0; p < a.push.n_ranks; ++p) reinterpret_cast<float *>(a.push.region[p] + h.dst_off)[at] = mine;
-                            }
-                            if (want_argmax && better(mine, row, best_v, best_i)) {
-                                best_v = mine;
-                                best_i = row;
-                            }
+                if constexpr (!kAligned) d0 = (d0 + SEG) & 15u;
+            }
+        }
+        if (expired) break;
+#ifdef VQM_NO_EPILOGUE
+        if (nrows > 1000) {
+#else
+        if (nrows > 0) {
+#endif
+            // lane r*M + t ends up holding y[t][row0 + r]
+            float sums[RW * M];
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+#pragma unroll
+                for (int t = 0; t < M; ++t) {
+                    float lo, hi;
+                    unpack2(acc[r][t], lo, hi);
+                    sums[r * M + t] = lo + hi;
+                    acc[r][t] = 0ull;
+                }
+            float mine = 0.0f;
+            if constexpr (RW * M > 16) {
+                mine = warp_sums(sums, lane);  // (measured: pays above 16 sums; below, its selects cost registers)
+            } else {
+#pragma unroll
+                for (int i = 0; i < RW * M; ++i) {
+                    const float s = warp_sum(sums[i]);
+                    if (lane == i) mine = s;
+                }
+            }
+            if (lane < RW * M) {
+                const int r = lane / M, t = lane % M, row = row0 + r;
+                if (r < nrows) {
+                    if (k_split > 1) {
+                        // this block's share of the columns only: it goes into the shared memory of the cluster's first
+                        // block, which adds the shares up (one-row chunks: r = 0, lane = t)
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&s_split[kpart][warp][t])), "r"(0));
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(mine) : "memory");
+                    } else {
+                        mine *= StepT::kOutScale;  // exact: 1 or a power of two (see bytes_to_subpair)
+                        const RowHome h = home_of(a, row);
+                        if (h.y != nullptr) h.y[static_cast<size_t>(t) * h.rows + h.local] = mine;
+                        if (a.push.push_slot > 0) {
+                            // row-sharded: the value also goes straight into every rank's gathered [M][rows_total] vector
+                            const size_t at = static_cast<size_t>(t) * h.rows_total + h.row_begin + h.local;
+                            for (int p = 0; p < a.push.n_ranks; ++p) reinterpret_cast<float *>(a.push.region[p] + h.dst_off)[at] = mine;
+                        }
+                        if (want_argmax && better(mine, row, best_v, best_i)) {
+                            best_v = mine;
+                            best_i = row;
                         }
                     }
                 }
             }
-            seg = 0;
-            row0 += nrows;
-            ++chunk;
-            nrows = chunk_base + (chunk < chunk_rem ? 1 : 0);
-        } else {
-            ++seg;
         }
-        if (active && ++stage == S) {
-            stage = 0;
-            phase ^= 1u;
-        }
-        if (++xstage == XS) {
-            xstage = 0;
-            xphase ^= 1u;
-        }
+        row0 += nrows;
     }
 
     if (expired) {
-        if (lane == 0) atomicExch(a.status, kStatusWaitExpired);
+        if (lane == 0) atomicCAS(a.status, 0u, kStatusWaitExpired);  // the first cause stays
         // give the copies still in flight into this warp's buffers one more bounded chance to land
         for (int s = 0; s < S; ++s) (void)mbar_wait_bounded(bar + s * 8, 0);
     }

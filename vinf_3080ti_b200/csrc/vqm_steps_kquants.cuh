@@ -2,9 +2,8 @@
 //
 // Common idea: the per-weight work is "raw field -> float" (one byte permute: the field becomes the subnormal
 // field * 2^-141, see bytes_to_subpair), one packed multiply or FMA per two weights with the group scale dl * 2^64
-// (exact: the product is the dequantised weight, without its minimum, times 2^-77) and one FMA per activation row.
-// The minimum of the types that carry one is taken out of the sum:
-//   sum_i (dl q_i - ml) x_i = sum_i (dl q_i) x_i - ml * sum_i x_i.
+// (exact: the result is the dequantised weight times 2^-77; the minimum of the types that carry one is the addend of
+// that same multiply-add, field * dl - ml, so it costs nothing) and one FMA per activation row.
 // Sub-scales are decoded once per step by a scale pass (word-wide mask arithmetic, four sub-scales per lane) into a
 // per-warp table of (dl, dl) pairs.  The sequence of operations per output does not depend on the number of
 // activation rows.
@@ -19,7 +18,7 @@ namespace vqm {
 // bytes 32p..32p+31 hold group 2p in their low and group 2p+1 in their high nibbles
 // (engine/csrc/common/qwen_quant.cuh:165-175).
 //   scale pass : lane -> (row, block, groups 4hh..4hh+3).  Per (row, block, pair of groups p) it leaves
-//                {dl, dl, dl'/16, dl'/16} and {-ml, -ml', 0, 0} (/16 because the high nibbles stay in place) in four
+//                {dl, dl, dl'/16, dl'/16} and {-ml, -ml, -ml', -ml'} (/16 because the high nibbles stay in place) in four
 //                "piece" arrays indexed by lane, so that its stores and the dot pass's loads are conflict-free.
 //   dot pass   : one block at a time, lane i -> 32-bit word i of the nibbles: 4 weights of group 2p (columns
 //                64p + 4(i%8) ..) and 4 of group 2p+1 (32 columns further), p = i / 8.  Eight lanes read 128
@@ -44,12 +43,10 @@ struct K45Step {
         static __device__ __forceinline__ void block_dot(uint32_t wl, uint32_t hl, int p, uint32_t el, uint32_t xl, f32x2 (&acc)[RW][M]) {
             constexpr int SLOT = slot_bytes(TYPE);
             X4 xa[M], xb[M];
-            f32x2 sx[M];
 #pragma unroll
             for (int t = 0; t < M; ++t) {
                 xa[t] = lds_x4(xl + t * kSegCols * 4);
                 xb[t] = lds_x4(xl + (t * kSegCols + 32) * 4);
-                sx[t] = pack2(sum_x4(xa[t]), sum_x4(xb[t]));
             }
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
@@ -63,15 +60,15 @@ struct K45Step {
                     lo = w & 0x0F0F0F0Fu;
                     hi = w & 0xF0F0F0F0u;  // 16 x the field; the scale table carries dl' / 16
                 }
-                const ulonglong2 dl = lds128(el + r * 128);           // (dl, dl), (dl', dl') [Q4_K: dl' / 16], each times 2^64
-                const f32x2 nml = lds64(el + r * 128 + kPiece);      // (-ml, -ml') times 2^-77
-                // exact products (at most 22 significant bits): the dequantised weights without their minimum, times 2^-77
-                const f32x2 a01 = mul2(bytes_to_subpair<0, 1>(lo), dl.x), a23 = mul2(bytes_to_subpair<2, 3>(lo), dl.x);
-                const f32x2 b01 = mul2(bytes_to_subpair<0, 1>(hi), dl.y), b23 = mul2(bytes_to_subpair<2, 3>(hi), dl.y);
+                const ulonglong2 dl = lds128(el + r * 128);            // (dl, dl), (dl', dl') [Q4_K: dl' / 16], each times 2^64
+                const ulonglong2 nm = lds128(el + r * 128 + kPiece);   // (-ml, -ml), (-ml', -ml'), each times 2^-77
+                // one fused multiply-add per pair: field * dl - ml, the dequantised weights times 2^-77 (the product is
+                // exact, so this is the single rounding of the reference's dl * q - ml)
+                const f32x2 a01 = fma2(bytes_to_subpair<0, 1>(lo), dl.x, nm.x), a23 = fma2(bytes_to_subpair<2, 3>(lo), dl.x, nm.x);
+                const f32x2 b01 = fma2(bytes_to_subpair<0, 1>(hi), dl.y, nm.y), b23 = fma2(bytes_to_subpair<2, 3>(hi), dl.y, nm.y);
 #pragma unroll
                 for (int t = 0; t < M; ++t)
-                    acc[r][t] = fma2(nml, sx[t], fma2(b23, xb[t].p23, fma2(b01, xb[t].p01,
-                                fma2(a23, xa[t].p23, fma2(a01, xa[t].p01, acc[r][t])))));
+                    acc[r][t] = fma2(b23, xb[t].p23, fma2(b01, xb[t].p01, fma2(a23, xa[t].p23, fma2(a01, xa[t].p01, acc[r][t]))));
             }
         }
 
@@ -92,9 +89,9 @@ struct K45Step {
                     const f32x2 dlo = pack2(d, d), dhi = pack2(dh, dh), mm = pack2(ndmin, ndmin);
                     const uint32_t dst = scratch + ((r * 4 + blk) * 2 + hh) * 16;
                     sts128(dst, mul2(bytes_to_pair<0, 0>(scw, neg_magic), dlo), mul2(bytes_to_pair<1, 1>(scw, neg_magic), dhi));
-                    sts128(dst + kPiece, mul2(bytes_to_pair<0, 1>(mnw, neg_magic), mm), 0ull);
+                    sts128(dst + kPiece, mul2(bytes_to_pair<0, 0>(mnw, neg_magic), mm), mul2(bytes_to_pair<1, 1>(mnw, neg_magic), mm));
                     sts128(dst + 2 * kPiece, mul2(bytes_to_pair<2, 2>(scw, neg_magic), dlo), mul2(bytes_to_pair<3, 3>(scw, neg_magic), dhi));
-                    sts128(dst + 3 * kPiece, mul2(bytes_to_pair<2, 3>(mnw, neg_magic), mm), 0ull);
+                    sts128(dst + 3 * kPiece, mul2(bytes_to_pair<2, 2>(mnw, neg_magic), mm), mul2(bytes_to_pair<3, 3>(mnw, neg_magic), mm));
                 }
             }
             __syncwarp();
