@@ -1,20 +1,29 @@
 """Benchmark of the GGUF quantized-matvec path:  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (N = 1): one decode pass over the synthetic 27B matvec set at M activation rows (default 4, the
-MTP k=3 verify pass): 64 layers x {Q6_K q/k/v/o, Q3_K gate/up, Q4_K down} with hidden 5120 / FFN 17408,
-then the Q6_K LM head 151936 x 5120 with the fused on-device argmax - 449 matvec launches over
-12.6 GB of raw GGUF blocks, all resident in HBM.  Weights are seeded synthetic blocks (uniform-random
-bytes, fp16 super-scales uniform in [1e-3, 1e-2)), activations fp32 N(0,1).  The pass is 100x larger than L2,
-so no flush is needed between steps.
+Workload: one decode pass over the synthetic 27B matvec set at M activation rows (default 4, the MTP k=3 verify
+pass): 64 layers x {Q6_K q/k/v/o, Q3_K gate/up, Q4_K down} with hidden 5120 / FFN 17408, then the Q6_K LM head
+151936 x 5120 with the fused on-device argmax - 257 launches (q/k/v and gate/up of a layer go out as one launch each)
+over 12.6 GB of raw GGUF blocks, all resident in HBM.  Weights are seeded synthetic blocks (uniform-random bytes,
+fp16 super-scales uniform in [1e-3, 1e-2)), activations fp32 N(0,1).  The pass is 100x larger than L2, so no flush is
+needed between steps.
 
-metric / value   weight GB/s of the pass (weight bytes / device time), kernel-side, inputs resident in HBM
-e2e              the same through the public Runtime API with host buffers: per step the activations are
-                 copied from pinned host memory, the pass runs, the argmax ids are read back
-roofline         the dominant kernel (Q3_K gate/up matvec) timed alone over the model's 128 distinct tensors
-cpu_baseline     the reference's own CPU matvec (oracle/_ref, built from the reference's qwen_cpu.c) on a
-                 bounded sample of the same pass, on this host's cores
-N > 1 (torchrun) every rank owns a contiguous slice of the output rows of every tensor (strong scaling); outputs
-                 are combined with NCCL all-gathers, the argmax with an all-gather of (value, index) pairs.
+One JSON line on rank 0:
+  metric / value   weight GB/s of the pass (weight bytes / device time), inputs resident in HBM, one CUDA graph per pass
+  e2e              the same with host buffers: per step the activations are copied from pinned host memory, the pass
+                   runs, the argmax ids are read back; `e2e.plugin_calls` times the call sequence the reference's
+                   executor makes (write -> qmv ... -> argmax_rows, one call per launch, no graph)
+  roofline         the dominant kernel (Q3_K gate/up matvec) timed alone over the model's 128 distinct tensors
+  kernels          the metric's first clause: single matvec kernels at M = 1 / 4 / 8 (and the IQ sweep at M = 1 / 8), each
+                   over enough distinct copies of its tensor to defeat L2
+  prefill          the prompt-pass GEMM, Q4_K 17408 x 5120 with 512 activation rows
+  reference_cuda_kernel   the reference's own CUDA matvec kernel (its source compiled unchanged for sm_100a) on the
+                   same tensors, same GPU
+  cpu_baseline     the reference's own CPU matvec on this host's cores, on the pass's byte mix
+N > 1 (torchrun)   every rank owns a contiguous slice of the output rows of every tensor (strong scaling); a matvec
+                   pushes its slice into every rank's gathered vector from its epilogue (default) or the slices are
+                   combined with NCCL all-gathers (--gather nccl).  `multi_gpu_check` compares the pushed vectors with
+                   NCCL all-gathers of the same slices and the combined argmax with the argmax of the gathered logits.
+--impl reference   the reference's CPU implementation alone, on the same byte mix (64 layer sets + the LM head per step)
 """
 from __future__ import annotations
 
@@ -35,20 +44,28 @@ sys.path.insert(0, str(REPO))
 
 from vinf_3080ti_b200.gguf_types import F16_FIELDS, TRAITS, GGUFTensorType as T  # noqa: E402
 from vinf_3080ti_b200.sharding import pick_best, shard_rows  # noqa: E402
-from vinf_3080ti_b200.synth import LAYER_SET, LM_HEAD, N_LAYERS, synthetic_activations, synthetic_blocks, tensor_bytes  # noqa: E402
+from vinf_3080ti_b200.synth import IQ_SWEEP, LAYER_SET, LM_HEAD, N_LAYERS, synthetic_activations, synthetic_blocks, tensor_bytes  # noqa: E402
 
 METRIC = "quant-matvec weight GB/s, synthetic-27B decode pass"
-# DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture (profiles/qmv_Q3_K_17408x5120_M4.md)
+# DRAM bytes (read + write) of one launch of the dominant kernel (Q3_K 17408 x 5120, M = 4) from an ncu capture
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 38447616
+SM_COUNT, SM_LANES, SM_MAX_HZ = 148, 128, 1.965e9
 
 
 # ---- helpers ---------------------------------------------------------------------------------------------
 
-def measured_peak_gbs() -> tuple[float, str]:
+def measured_peaks() -> dict:
     path = REPO / "MEASURED_PEAKS.json"
     if path.exists():
-        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        d = json.loads(path.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def fma_ceiling_gbs(t: T, m: int) -> float:
+    """Weight GB/s at which one fp32 FMA per weight per activation row saturates the fp32 pipe (148 SMs x 128 lanes)."""
+    block, size = TRAITS[t]
+    return SM_COUNT * SM_LANES * SM_MAX_HZ / m * (size / block) / 1e9
 
 
 class ClockSampler:
@@ -106,46 +123,80 @@ def pass_tensors() -> list[tuple[str, T, int, int]]:
     return out
 
 
+def codebooks() -> dict[str, bytes]:
+    with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
+        return {k: z[k].tobytes() for k in z.files}
+
+
 # ---- the CPU arm -----------------------------------------------------------------------------------------
 
-class CpuArm:
-    """The reference's own CPU matvec (oracle/_ref, compiled from the reference's qwen_cpu.c) on a bounded sample
-    of the pass: one layer set (7 tensors) + the Q6_K LM head.  Falls back to the plain-C oracle port only if
-    the reference build is missing."""
+def cpu_weights(distinct: int = 4) -> dict:
+    """Host copies of `distinct` layer sets and the LM head (seeded synthetic blocks)."""
+    rng = np.random.default_rng(0)
+    sets = [[(name, t, rows, cols, synthetic_blocks(t, rows, cols, rng)) for name, t, rows, cols in LAYER_SET] for _ in range(distinct)]
+    name, t, rows, cols = LM_HEAD
+    return {"sets": sets, "head": (name, t, rows, cols, synthetic_blocks(t, rows, cols, rng))}
 
-    def __init__(self, m: int, threads: int) -> None:
+
+class CpuArm:
+    """The reference's own CPU matvec (oracle/_ref, compiled from the reference's qwen_cpu.c) on the pass's byte mix: the
+    seven tensors of a layer 64 times, then the Q6_K LM head once.  Several distinct layer sets are held in memory and
+    taken in turn, so that consecutive layers do not find their weights in the host's caches.  Falls back to the
+    plain-C oracle port (OpenMP over rows) only if the reference build is missing."""
+
+    def __init__(self, m: int, threads: int, weights: dict, layers: int = N_LAYERS) -> None:
         from tests import oracle_libs
 
-        self.m, self.threads = m, threads
+        self.m, self.layers = m, layers
         mod = oracle_libs.load_reference_cpu_module()
         self.kind = "reference" if mod is not None else "port"
-        with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
-            grid = z["iq3s_grid"].tobytes()
-        rng = np.random.default_rng(0)
-        sample = list(LAYER_SET) + [LM_HEAD]
-        self.nbytes = 0
-        self.keep = []
+        rng = np.random.default_rng(1)
+        sets, head = weights["sets"], weights["head"]
+        distinct = len(sets)
+        self.nbytes = layers * sum(tensor_bytes(t, r, c) for _, t, r, c in LAYER_SET) + tensor_bytes(*LM_HEAD[1:])
+        xs = {name: synthetic_activations(m, cols, rng) for name, _, _, cols in LAYER_SET}
+        x_head = synthetic_activations(m, head[3], rng)
         if mod is not None:
-            rt = mod.CpuRuntime(grid, threads)
-            for name, t, rows, cols in sample:
-                raw = synthetic_blocks(t, rows, cols, rng).tobytes()
-                self.keep.append(raw)
-                rt.add_tensor(name, raw, int(t), cols, rows)
-                rt.alloc(name + ".x", m * cols)
-                rt.alloc(name + ".y", m * rows)
-                rt.write(name + ".x", synthetic_activations(m, cols, rng).tobytes())
-                self.nbytes += len(raw)
-            self._pass = lambda: [rt.qmv(name, name + ".x", name + ".y", m) for name, *_ in sample]
+            rt = mod.CpuRuntime(codebooks()["iq3s_grid"], threads)
+            self.threads_used = threads if threads > 0 else max(1, (os.cpu_count() or 2) // 2)  # its default: half the processors
+            self.keep = []
+            for name, t, rows, cols in LAYER_SET:
+                rt.alloc(f"{name}.x", m * cols)
+                rt.alloc(f"{name}.y", m * rows)
+                rt.write(f"{name}.x", xs[name].tobytes())
+            for k, layer_set in enumerate(sets):
+                for name, t, rows, cols, raw in layer_set:
+                    data = raw.tobytes()
+                    self.keep.append(data)
+                    rt.add_tensor(f"{k}.{name}", data, int(t), cols, rows)
+            name, t, rows, cols, raw = head
+            data = raw.tobytes()
+            self.keep.append(data)
+            rt.add_tensor(name, data, int(t), cols, rows)
+            rt.alloc("lm.x", m * cols)
+            rt.alloc("lm.y", m * rows)
+            rt.write("lm.x", x_head.tobytes())
+
+            def one_pass() -> None:
+                for layer in range(layers):
+                    k = layer % distinct
+                    for tname, *_ in LAYER_SET:
+                        rt.qmv(f"{k}.{tname}", f"{tname}.x", f"{tname}.y", m)
+                rt.qmv(LM_HEAD[0], "lm.x", "lm.y", m)
         else:
             clib = oracle_libs.load_c_oracle()
-            mats = []
-            for name, t, rows, cols in sample:
-                raw = synthetic_blocks(t, rows, cols, rng)
-                mats.append((raw, t, rows, cols, synthetic_activations(m, cols, rng)))
-                self.nbytes += raw.size
-            self._pass = lambda: [oracle_libs.c_qmv(clib, raw, int(t), rows, cols, x) for raw, t, rows, cols, x in mats]
-        self.sample = (f"one layer set (Q6_K q/k/v/o, Q3_K gate/up, Q4_K down) + the Q6_K LM head at M={m}, "
-                       f"{self.nbytes} weight bytes per pass")
+            self.threads_used = os.cpu_count() or 1
+
+            def one_pass() -> None:
+                for layer in range(layers):
+                    for name, t, rows, cols, raw in sets[layer % distinct]:
+                        oracle_libs.c_qmv(clib, raw, int(t), rows, cols, xs[name])
+                name, t, rows, cols, raw = head
+                oracle_libs.c_qmv(clib, raw, int(t), rows, cols, x_head)
+
+        self._pass = one_pass
+        self.sample = (f"the pass's byte mix at M={m}: {layers} x (Q6_K q/k/v/o, Q3_K gate/up, Q4_K down; {distinct} distinct layer sets in turn) "
+                       f"+ the Q6_K LM head, {self.nbytes} weight bytes per step")
 
     def one_pass(self) -> float:
         t0 = time.perf_counter()
@@ -154,80 +205,198 @@ class CpuArm:
 
 
 def cpu_baseline(m: int, seconds: float) -> dict:
-    threads = os.cpu_count() or 1
-    arm = CpuArm(m, threads)
+    """The reference CPU path on a bounded number of passes: all host threads, then the reference's own default
+    (half the processors, engine/csrc/cpu/qwen_cpu.c:438) for a few passes beside it."""
+    nproc = os.cpu_count() or 1
+    weights = cpu_weights()
+    arm = CpuArm(m, nproc, weights)
     arm.one_pass()
     times = []
     t_end = time.perf_counter() + seconds
     while time.perf_counter() < t_end or len(times) < 2:
         times.append(arm.one_pass())
-    return {"value": arm.nbytes / min(times) / 1e9, "unit": "GB/s", "cores": threads, "kind": arm.kind,
-            "sample": f"{arm.sample}; best of {len(times)} passes in ~{seconds:.0f} s"}
-
-
-def reference_cuda_kernel(m: int) -> dict | None:
-    """Part of the baseline leg: the reference's own CUDA matvec kernel (its qwen_runtime.cu compiled unchanged for
-    sm_100a into oracle/_ref) timed on this GPU on the tensor of the roofline leg, Q3_K 17408 x 5120, over 4 copies
-    (153 MB, larger than L2).  None if that module has not been built."""
-    import importlib.util
-
-    import torch
-
-    path = REPO / "oracle" / "_ref" / "_cuda_qwen_runtime.so"
-    if not path.exists():
-        return None
-    spec = importlib.util.spec_from_file_location("_cuda_qwen_runtime", path)
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
-        ref = mod.Runtime(z["iq3s_grid"].tobytes())
-    rows, cols, copies = 17408, 5120, 4
-    rng = np.random.default_rng(0)
-    raw = synthetic_blocks(T.Q3_K, rows, cols, rng).tobytes()
-    for i in range(copies):
-        ref.upload(f"w{i}", raw, int(T.Q3_K), cols, rows)
-    ref.alloc("x", m * cols)
-    ref.alloc("y", m * rows)
-    ref.write("x", synthetic_activations(m, cols, rng).tobytes())
-    stream = torch.cuda.default_stream()  # the reference launches on the legacy default stream
-    best = float("inf")
-    for rep in range(4):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(copies):
-            ref.qmv(f"w{i}", "x", "y", m)
-        e1.record(stream)
-        ref.synchronize()
-        if rep:
-            best = min(best, e0.elapsed_time(e1) / copies)
-    for i in range(copies):
-        ref.free(f"w{i}")
-    return {"kernel": "reference vinf_qmatvec_kernel rebuilt for sm_100a, Q3_K 17408x5120", "us_per_launch": best * 1e3,
-            "weight_GBs": len(raw) / (best * 1e-3) / 1e9}
+    out = {"value": arm.nbytes / min(times) / 1e9, "median": arm.nbytes / statistics.median(times) / 1e9, "unit": "GB/s", "cores": arm.threads_used,
+           "kind": arm.kind, "sample": f"{arm.sample}; best (value) and median of {len(times)} passes in ~{seconds:.0f} s"}
+    if arm.kind == "reference":
+        del arm
+        half = CpuArm(m, 0, weights)
+        half.one_pass()
+        ht = [half.one_pass() for _ in range(3)]
+        out["reference_default_threads"] = {"value": half.nbytes / min(ht) / 1e9, "median": half.nbytes / statistics.median(ht) / 1e9,
+                                            "cores": half.threads_used, "note": "threads = 0: the reference's default, half the processors"}
+    return out
 
 
 def run_reference(args) -> None:
     """--impl reference: the reference's CPU implementation of the path on this host's cores.  Rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    threads = os.cpu_count() or 1
-    arm = CpuArm(args.m, threads)
-    for _ in range(max(1, args.warmup)):
+    nproc = os.cpu_count() or 1
+    arm = CpuArm(args.m, nproc, cpu_weights())
+    warmup = max(1, args.warmup)
+    for _ in range(warmup):
         arm.one_pass()
     times = [arm.one_pass() for _ in range(args.steps)]
     ms = 1e3 * sum(times) / len(times)
     value = arm.nbytes / (ms * 1e-3) / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": max(1, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32 outputs; the reference CPU kernel rounds activations to int8 per 32 elements", "data": "synthetic",
-        "config": {"workload": f"synthetic-27B decode pass at M={args.m}; each step is a bounded sample of it: {arm.sample}",
-                   "activation_rows": args.m},
-        "tokens_per_s": None,
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": arm.kind, "sample": arm.sample},
+        "config": {"workload": f"synthetic-27B decode pass at M={args.m}: {arm.sample}", "activation_rows": args.m},
+        "tokens_per_s": args.m / (ms * 1e-3),
+        "cpu_baseline": {"value": value, "median": arm.nbytes / statistics.median(times) / 1e9, "best": arm.nbytes / min(times) / 1e9, "unit": "GB/s",
+                         "cores": arm.threads_used, "kind": arm.kind, "sample": arm.sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+# ---- single kernels, the prompt GEMM and the reference's CUDA kernel (rank 0 of a one-GPU run) ---------------------
+
+KERNEL_CASES = [(T.Q4_K, 17408, 5120, (1, 4, 8)), (T.Q6_K, 6144, 5120, (1, 4, 8)), (T.IQ4_XS, 17408, 5120, (1, 4, 8)), (T.Q3_K, 17408, 5120, (1, 4, 8))] + \
+               [(t, r, c, (1, 8)) for t, r, c in IQ_SWEEP if t is not T.IQ4_XS]
+
+
+def device_blocks(torch, t: T, rows: int, cols: int, gen, dev):
+    """Seeded synthetic raw blocks of a rows x cols tensor, generated on the device (+256 bytes of readable padding)."""
+    block, size = TRAITS[t]
+    nblk = rows * (cols // block)
+    raw = torch.randint(0, 256, (nblk * size + 256,), dtype=torch.uint8, device=dev, generator=gen)
+    blocks = raw[: nblk * size].view(nblk, size)
+    for off in F16_FIELDS[t]:
+        scale = torch.empty(nblk, dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=gen).to(torch.float16)
+        blocks[:, off : off + 2] = scale.view(torch.uint8).view(nblk, 2)
+    return raw, nblk * size
+
+
+def time_events(torch, stream, fn, reps: int) -> list[float]:
+    out = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        fn()
+        e1.record(stream)
+        stream.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return out
+
+
+def kernel_table(rt, torch, stream, dev, peaks: dict) -> list[dict]:
+    """Every case: a CUDA graph of one launch per distinct copy of the tensor (more than 2 x L2 of weights in all), CUDA
+    events around the graph, best and median of 7 after 3 warm-up replays."""
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+    rows_out = []
+    for t, rows, cols, ms in KERNEL_CASES:
+        nbytes = tensor_bytes(t, rows, cols)
+        copies = max(8, -(-300_000_000 // nbytes))
+        keep = []
+        for i in range(copies):
+            raw, _ = device_blocks(torch, t, rows, cols, gen, dev)
+            keep.append(raw)
+            rt.bind_tensor(f"k{i}", raw.data_ptr(), int(t), cols, rows)
+        x = torch.randn(8 * cols, dtype=torch.float32, device=dev, generator=gen)
+        y = torch.empty(8 * rows, dtype=torch.float32, device=dev)
+        rt.bind("kx", x.data_ptr(), 8 * cols)
+        rt.bind("ky", y.data_ptr(), 8 * rows)
+        for m in ms:
+            rt.qmv("k0", "kx", "ky", m)  # first use outside of capture
+            rt.synchronize()
+            rt.capture_begin()
+            for i in range(copies):
+                rt.qmv(f"k{i}", "kx", "ky", m)
+            graph = rt.capture_end()
+            for _ in range(3):
+                rt.graph_launch(graph)
+            times = time_events(torch, stream, lambda: rt.graph_launch(graph), 7)
+            rt.graph_destroy(graph)
+            us = min(times) * 1e3 / copies
+            gbs = nbytes / us / 1e3
+            ceiling = min(peaks["hbm_gbs"], fma_ceiling_gbs(t, m))
+            rows_out.append({"tensor": f"{t.name} {rows}x{cols}", "M": m, "us": round(us, 2), "us_median": round(statistics.median(times) * 1e3 / copies, 2),
+                             "weight_GBs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBs": round(gbs / 8000.0, 4),
+                             "frac_of_min_hbm_fma": round(gbs / ceiling, 4), "copies": copies})
+        for i in range(copies):
+            rt.free(f"k{i}")
+        rt.release("kx")
+        rt.release("ky")
+        del keep, x, y
+    return rows_out
+
+
+def prefill_gemm(rt, torch, stream, dev, peaks: dict) -> dict:
+    """The prompt pass: Q4_K 17408 x 5120 with 512 activation rows through the tensor-core GEMM (set_gemm_min_rows)."""
+    t, rows, cols, ntok = T.Q4_K, 17408, 5120, 512
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(512)
+    raw, _ = device_blocks(torch, t, rows, cols, gen, dev)
+    rt.bind_tensor("pw", raw.data_ptr(), int(t), cols, rows)
+    x = torch.randn(ntok * cols, dtype=torch.float32, device=dev, generator=gen)
+    y = torch.empty(ntok * rows, dtype=torch.float32, device=dev)
+    rt.bind("px", x.data_ptr(), ntok * cols)
+    rt.bind("py", y.data_ptr(), ntok * rows)
+    rt.set_gemm_min_rows(64)
+    try:
+        for _ in range(3):
+            rt.qmv("pw", "px", "py", ntok)
+        rt.synchronize()
+        times = time_events(torch, stream, lambda: rt.qmv("pw", "px", "py", ntok), 7)
+    finally:
+        rt.set_gemm_min_rows(0)
+    rt.free("pw")
+    rt.release("px")
+    rt.release("py")
+    ms = min(times)
+    flops = 2.0 * ntok * rows * cols
+    return {"tensor": f"{t.name} {rows}x{cols}", "activation_rows": ntok, "ms": round(ms, 4), "ms_median": round(statistics.median(times), 4),
+            "TFLOPs": round(flops / ms / 1e9, 1), "frac_of_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4),
+            "note": "fp32 activations -> fp16, weights dequantised to fp16 tiles, tcgen05 MMA with fp32 accumulators in tensor memory; "
+                    "time includes the fp32 -> fp16 conversion of the activations"}
+
+
+def reference_cuda_kernels(torch, dev, ours: list[dict]) -> dict:
+    """The reference's own CUDA matvec kernel (its qwen_runtime.cu compiled unchanged for sm_100a into oracle/_ref), launched by
+    its own runtime on its stream, on the four main tensors at M = 1 / 4 / 8 over 4 distinct copies (> L2)."""
+    import importlib.util
+
+    path = REPO / "oracle" / "_ref" / "_cuda_qwen_runtime.so"
+    if not path.exists():
+        return {"unavailable": "oracle/_ref/_cuda_qwen_runtime.so has not been built"}
+    spec = importlib.util.spec_from_file_location("_cuda_qwen_runtime", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    ref = mod.Runtime(codebooks()["iq3s_grid"])
+    stream = torch.cuda.default_stream()  # the reference launches on the legacy default stream
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    mine = {(r["tensor"], r["M"]): r["us"] for r in ours}
+    out = []
+    for t, rows, cols, ms in KERNEL_CASES[:4]:
+        nbytes = tensor_bytes(t, rows, cols)
+        copies = max(4, -(-160_000_000 // nbytes))
+        for i in range(copies):
+            raw, n = device_blocks(torch, t, rows, cols, gen, dev)
+            ref.upload(f"w{i}", raw[:n].cpu().numpy().tobytes(), int(t), cols, rows)
+        ref.alloc("x", 8 * cols)
+        ref.alloc("y", 8 * rows)
+        ref.write("x", synthetic_activations(8, cols, np.random.default_rng(1)).tobytes())
+        for m in ms:
+            def run() -> None:
+                for i in range(copies):
+                    ref.qmv(f"w{i}", "x", "y", m)
+            run()
+            ref.synchronize()
+            times = time_events(torch, stream, run, 4)
+            us = min(times) * 1e3 / copies
+            row = {"tensor": f"{t.name} {rows}x{cols}", "M": m, "us": round(us, 2), "weight_GBs": round(nbytes / us / 1e3, 1)}
+            if (row["tensor"], m) in mine:
+                row["this_library_us"] = mine[(row["tensor"], m)]
+                row["this_library_speedup"] = round(us / mine[(row["tensor"], m)], 2)
+            out.append(row)
+        for i in range(copies):
+            ref.free(f"w{i}")
+    return {"kernel": "vinf_qmatvec_kernel (engine/csrc/megakernel/qwen_runtime.cu:579-628), unchanged source, -arch=sm_100a", "rows": out}
 
 
 # ---- the GPU arm -----------------------------------------------------------------------------------------
@@ -246,46 +415,38 @@ def run_gpu(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     m = args.m
-    with np.load(REPO / "tests" / "golden" / "iq_codebooks.npz") as z:
-        books = {k: z[k].tobytes() for k in z.files}
+    books = codebooks()
     rt = Runtime(books["iq3s_grid"], books)
     # the runtime launches on a stream torch owns, so that torch events, copies and NCCL order against it
     stream = torch.cuda.Stream(device=dev)
     rt.set_stream(stream.cuda_stream)
+    peaks = measured_peaks()
 
     # -- weights: seeded synthetic blocks generated on the device, this rank's row slice of every tensor
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     keep = []
-    weight_bytes_local = 0
     weight_bytes_total = 0
     tensors = pass_tensors()
     local_rows: dict[str, tuple[int, int]] = {}
     for name, t, rows, cols in tensors:
         begin, end = shard_rows(rows, rank, world)
-        n = end - begin
-        block, size = TRAITS[t]
-        nblk = n * (cols // block)
-        raw = torch.randint(0, 256, (nblk * size + 256,), dtype=torch.uint8, device=dev, generator=gen)
-        blocks = raw[: nblk * size].view(nblk, size)
-        for off in F16_FIELDS[t]:
-            scale = torch.empty(nblk, dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=gen).to(torch.float16)
-            blocks[:, off : off + 2] = scale.view(torch.uint8).view(nblk, 2)
+        raw, _ = device_blocks(torch, t, end - begin, cols, gen, dev)
         keep.append(raw)
-        rt.bind_tensor(name, raw.data_ptr(), int(t), cols, n)
+        rt.bind_tensor(name, raw.data_ptr(), int(t), cols, end - begin)
         local_rows[name] = (begin, end)
-        weight_bytes_local += nblk * size
         weight_bytes_total += tensor_bytes(t, rows, cols)
     rt.set_argmax_row_base(LM_HEAD[0], local_rows[LM_HEAD[0]][0])
 
     # -- activations and outputs.  The synthetic pass has no ops between the matvecs, so every matvec of a given
-    #    input width reads the same activation buffer; outputs of all ranks are gathered into full-width buffers.
+    #    input width reads the same activation buffer (the check pass of a multi-GPU run chains them instead).
     widths = sorted({cols for _, _, _, cols in tensors})
     host_x = {w: torch.from_numpy(synthetic_activations(m, w, np.random.default_rng(w))).pin_memory() for w in widths}
     dev_x = {w: torch.empty(m * w, dtype=torch.float32, device=dev) for w in widths}
     for w in widths:
         rt.bind(f"x{w}", dev_x[w].data_ptr(), m * w)
         dev_x[w].copy_(host_x[w].view(-1))
+
     def kind_of(name: str) -> str:
         return name.split(".")[-1]
 
@@ -294,7 +455,7 @@ def run_gpu(args) -> None:
         return e - b
 
     # per kind of tensor: this rank's [M][rows of the slice] block, padded to the widest slice so that one
-    # all_gather_into_tensor of equal-sized chunks combines the ranks (NCCL arm)
+    # all_gather_into_tensor of equal-sized chunks combines the ranks (NCCL arm and the check)
     kind_rows = {kind_of(name): rows for name, _, rows, _ in tensors}
     widest = {k: max(slice_rows(r, i) for i in range(world)) for k, r in kind_rows.items()}
     y_local = {k: torch.zeros(m * widest[k], dtype=torch.float32, device=dev) for k in kind_rows}
@@ -316,44 +477,40 @@ def run_gpu(args) -> None:
         else:
             launches_of_pass.append([entry])
 
-    def enqueue_pass() -> None:
-        for group in launches_of_pass[:-1]:
-            cols = group[0][3]
-            if len(group) == 1:
-                rt.qmv(group[0][0], f"x{cols}", f"y.{kind_of(group[0][0])}", m)
-            else:
-                rt.qmv_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m)
-        name, t, rows, cols = launches_of_pass[-1][0]
-        rt.qmv_argmax(name, f"x{cols}", f"y.{kind_of(name)}", m, blocking=False)
+    def enqueue_launch(group, fused_argmax: bool = False) -> None:
+        cols = group[0][3]
+        if fused_argmax:
+            rt.qmv_argmax(group[0][0], f"x{cols}", f"y.{kind_of(group[0][0])}", m, blocking=False)
+        elif len(group) == 1:
+            rt.qmv(group[0][0], f"x{cols}", f"y.{kind_of(group[0][0])}", m)
+        else:
+            rt.qmv_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m)
 
-    # single GPU: the whole pass is one CUDA graph; multi GPU: kernels on the runtime's stream, gathers after each
-    graph = None
-    if world == 1:
-        enqueue_pass()  # sets the kernels' attributes outside of capture
-        rt.synchronize()
-        rt.capture_begin()
-        enqueue_pass()
-        graph = rt.capture_end()
-
-    def sharded_pass() -> None:  # NCCL arm: kernel, all-gather(s), kernel, ... launched eagerly
+    def enqueue_pass() -> None:  # this rank's kernels alone: the whole pass on one GPU, the "exchange off" figure on several
         for group in launches_of_pass[:-1]:
-            cols = group[0][3]
-            if len(group) == 1:
-                rt.qmv(group[0][0], f"x{cols}", f"y.{kind_of(group[0][0])}", m)
-            else:
-                rt.qmv_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m)
+            enqueue_launch(group)
+        enqueue_launch(launches_of_pass[-1], fused_argmax=True)
+
+    enqueue_pass()  # sets the kernels' attributes outside of capture
+    rt.synchronize()
+    rt.capture_begin()
+    enqueue_pass()
+    local_graph = rt.capture_end()
+
+    def nccl_pass() -> None:  # NCCL arm: kernel, all-gather(s), kernel, ... launched eagerly
+        for group in launches_of_pass[:-1]:
+            enqueue_launch(group)
             for e in group:
                 dist.all_gather_into_tensor(gathered[kind_of(e[0])], y_local[kind_of(e[0])])
-        name, t, rows, cols = launches_of_pass[-1][0]
-        rt.qmv_argmax(name, f"x{cols}", f"y.{kind_of(name)}", m, blocking=False)
-        dist.all_gather_into_tensor(gathered[kind_of(name)], y_local[kind_of(name)])
+        enqueue_launch(launches_of_pass[-1], fused_argmax=True)
+        dist.all_gather_into_tensor(gathered["output"], y_local["output"])
 
     # Fused arm (default): every matvec pushes its slice into the gathered vector of every rank from its own epilogue and
     # the next matvec waits for all ranks' flags - the dependency chain of a tensor-parallel decoder.  One gathered
     # vector per kind of tensor (q, k, v, o, gate, up, down, logits); one flag slot per launch of the pass; the whole
     # pass is one CUDA graph per rank and contains no collective.
     use_push = world > 1 and args.gather == "push"
-    push_mode = os.environ.get("VINF_BENCH_PUSH_MODE", "full")  # experiments: "nowait" (push, no flag waits), "none" (sharded kernels only)
+    push_graph = None
     if use_push:
         from vinf_3080ti_b200.sharding import ExchangeLayout, connect_exchange
 
@@ -364,7 +521,9 @@ def run_gpu(args) -> None:
                 kinds[kind_of(name)] = off
                 off += (4 * m * rows + 255) // 256 * 256
         layout = ExchangeLayout(off, n_slots=len(launches_of_pass))
-        connect_exchange(rt, layout)
+        region_addrs = connect_exchange(rt, layout)
+        for k, at in kinds.items():  # the gathered vectors inside this rank's own region, as buffers
+            rt.bind(f"g.{k}", region_addrs[rank] + at, m * kind_rows[k])
 
         # the launch whose flags a launch waits for: the last one that produced (part of) its input
         producer_kind = {"attn_q": "ffn_down", "attn_o": "attn_v", "ffn_gate": "attn_o", "ffn_up": "attn_o", "ffn_down": "ffn_up",
@@ -377,38 +536,39 @@ def run_gpu(args) -> None:
             for e in group:
                 last_of_kind[kind_of(e[0])] = i
 
+        def push_launch(i: int, x_of: dict | None = None) -> None:
+            """Launch i of the pass with its push; x_of maps an input width to the buffer to read instead of the local one."""
+            group = launches_of_pass[i]
+            cols = group[0][3]
+            x_name = (x_of or {}).get(kind_of(group[0][0]), f"x{cols}")  # keyed by the kind of the launch's first tensor
+            if len(group) == 1:
+                name, t, rows, _ = group[0]
+                rt.qmv_push(name, x_name, f"y.{kind_of(name)}", m, slot=i, dst_off=kinds[kind_of(name)], rows_total=rows,
+                            row_begin=local_rows[name][0], wait_slot=wait_for[i], with_argmax=(i == len(launches_of_pass) - 1))
+            else:
+                rt.qmv_push_group([e[0] for e in group], x_name, [f"y.{kind_of(e[0])}" for e in group], m, slot=i,
+                                  dst_offs=[kinds[kind_of(e[0])] for e in group], rows_totals=[e[2] for e in group],
+                                  row_begins=[local_rows[e[0]][0] for e in group], wait_slot=wait_for[i])
+
         def push_pass() -> None:
-            for i, group in enumerate(launches_of_pass):
-                cols = group[0][3]
-                slot = i if push_mode != "none" else -1
-                wait_slot = wait_for[i] if push_mode == "full" else -1
-                if len(group) == 1:
-                    name, t, rows, _ = group[0]
-                    rt.qmv_push(name, f"x{cols}", f"y.{kind_of(name)}", m, slot=slot, dst_off=kinds[kind_of(name)], rows_total=rows,
-                                row_begin=local_rows[name][0], wait_slot=wait_slot, with_argmax=(i == len(launches_of_pass) - 1))
-                else:
-                    rt.qmv_push_group([e[0] for e in group], f"x{cols}", [f"y.{kind_of(e[0])}" for e in group], m, slot=slot,
-                                      dst_offs=[kinds[kind_of(e[0])] for e in group], rows_totals=[e[2] for e in group],
-                                      row_begins=[local_rows[e[0]][0] for e in group], wait_slot=wait_slot)
+            for i in range(len(launches_of_pass)):
+                push_launch(i)
 
         push_pass()
         rt.synchronize()
         dist.barrier()
         rt.capture_begin()
         push_pass()
-        graph = rt.capture_end()
-
-    torch_graph = None
+        push_graph = rt.capture_end()
 
     def device_pass() -> None:
-        if world == 1 or use_push:
-            rt.graph_launch(graph)
-        elif torch_graph is not None:
-            with torch.cuda.stream(stream):
-                torch_graph.replay()
+        if world == 1:
+            rt.graph_launch(local_graph)
+        elif use_push:
+            rt.graph_launch(push_graph)
         else:
             with torch.cuda.stream(stream):
-                sharded_pass()
+                nccl_pass()
 
     def barrier() -> None:
         if world > 1:
@@ -441,6 +601,15 @@ def run_gpu(args) -> None:
         rt.bind("argmax.vals", vals_addr, 8)
         rt.bind("argmax.ids", ids_addr, 8)
 
+    def combined_ids() -> list[int]:
+        rt.copy("argmax.pair", 0, "argmax.vals", 0, m)
+        rt.copy("argmax.pair", 8, "argmax.ids", 0, m)
+        with torch.cuda.stream(stream):
+            dist.all_gather_into_tensor(pairs, pair)
+            pairs_host.copy_(pairs, non_blocking=True)
+        stream.synchronize()
+        return pick_best(pairs_host[:, 0, :m].to(torch.float64), pairs_host[:, 1, :m].contiguous().view(torch.int32).to(torch.int64)).tolist()
+
     def e2e_step() -> None:
         with torch.cuda.stream(stream):
             for w in widths:
@@ -448,14 +617,19 @@ def run_gpu(args) -> None:
         device_pass()
         if world == 1:
             rt.argmax_fetch(m, with_values=True)
-            return
-        rt.copy("argmax.pair", 0, "argmax.vals", 0, m)
-        rt.copy("argmax.pair", 8, "argmax.ids", 0, m)
-        with torch.cuda.stream(stream):
-            dist.all_gather_into_tensor(pairs, pair)
-            pairs_host.copy_(pairs, non_blocking=True)
-        stream.synchronize()
-        pick_best(pairs_host[:, 0, :m].to(torch.float64), pairs_host[:, 1, :m].contiguous().view(torch.int32).to(torch.int64)).tolist()
+        else:
+            combined_ids()
+
+    # The same step through the calls the reference's executor makes on its runtime: write the activations from host
+    # memory, one qmv / qmv_group call per launch (no graph), argmax_rows over the stored logits (blocking, ids to the host).
+    host_np = {w: host_x[w].numpy() for w in widths}
+
+    def plugin_step() -> None:
+        for w in widths:
+            rt.write(f"x{w}", host_np[w])
+        for group in launches_of_pass:
+            enqueue_launch(group)
+        rt.argmax_rows("y.output", kind_rows["output"], m)
 
     # -- warm-up, then the timed regions
     for _ in range(max(3, args.warmup)):
@@ -466,10 +640,28 @@ def run_gpu(args) -> None:
         sampler.start()
     ms = timed(device_pass, args.steps)
     launches = rt.launch_count() - launches_before
-    if torch_graph is not None:
-        launches = args.steps * len(launches_of_pass)  # replayed by torch's graph, not counted by the runtime
     e2e_ms = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else {}
+    plugin_ms = None
+    if world == 1:
+        plugin_step()
+        plugin_ms = timed(plugin_step, max(2, args.steps // 4))
+
+    # -- multi-GPU: what the exchange costs, and whether what it delivers is right
+    scaling_detail = None
+    check = None
+    if world > 1:
+        scaling_detail = {"exchange_off_ms": timed(lambda: rt.graph_launch(local_graph), max(2, args.steps // 2)),
+                          "note": "exchange_off: this rank's sharded kernels alone (no push, no waits, one graph)"}
+        if use_push:
+            def nccl_step() -> None:
+                with torch.cuda.stream(stream):
+                    nccl_pass()
+
+            nccl_step()
+            scaling_detail["nccl_allgather_ms"] = timed(nccl_step, max(2, args.steps // 4))
+            check = multi_gpu_check(torch, dist, rt, stream, dev, m, rank, world, launches_of_pass, kind_of, kind_rows, widest, slice_rows,
+                                    y_local, gathered, push_launch, combined_ids)
 
     # -- roofline of the dominant kernel: the Q3_K gate/up matvec alone over the model's distinct tensors
     dom = [(n, t, r, c) for n, t, r, c in tensors if t is T.Q3_K]
@@ -482,16 +674,13 @@ def run_gpu(args) -> None:
     dominant()
     dom_ms = timed(dominant, max(2, args.steps // 2)) / len(dom)
     alg_bytes = d_rows * (dom[0][3] // 256) * 110 + 4 * m * dom[0][3] + 4 * m * d_rows
-    peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (dom_ms * 1e-3) / 1e9
-    # second bound: one fp32 FMA per weight per activation row on 148 SMs x 128 lanes at the maximum SM clock
-    fma_ceiling = 148 * 128 * 1.965e9 / m * (110 / 256) / 1e9  # weight GB/s at which the FMA pipe alone saturates
+    fma_ceiling = fma_ceiling_gbs(T.Q3_K, m)
 
     if rank == 0:
         value = weight_bytes_total / (ms * 1e-3) / 1e9
         e2e_value = weight_bytes_total / (e2e_ms * 1e-3) / 1e9
         h2d = sum(4 * m * w for w in widths)
-        cpu = cpu_baseline(m, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -505,30 +694,107 @@ def run_gpu(args) -> None:
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * m if world == 1 else 64 * world,
                     "tokens_per_s": m / (e2e_ms * 1e-3)},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (m == 4 and world == 1) else None, "kernel": f"qmv_kernel<Q3_K, M={m}> {d_rows}x{dom[0][3]}",
-                         "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": dom_ms * 1e3, "peak_source": f"of {peak_kind}",
-                         "fp32_fma_ceiling": {"weight_GBs": fma_ceiling, "frac": achieved / min(peak, fma_ceiling),
+                         "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": dom_ms * 1e3, "peak_source": f"of {peaks['source']}",
+                         "fp32_fma_ceiling": {"weight_GBs": fma_ceiling, "frac": achieved / min(peaks["hbm_gbs"], fma_ceiling),
                                               "note": "achieved / min(HBM peak, rate at which one FMA per weight per activation row saturates the fp32 pipe)"}},
             "clocks": clocks,
         }
-        if cpu is not None:
+        if plugin_ms is not None:
+            line["e2e"]["plugin_calls"] = {"value": weight_bytes_total / (plugin_ms * 1e-3) / 1e9, "ms_per_step": plugin_ms,
+                                           "calls": "write x3, qmv / qmv_group x257, argmax_rows (blocking): one call per launch, no graph, "
+                                                    "activations from host memory, ids to the host",
+                                           "d2h_bytes_per_step": 4 * m}
+        if scaling_detail is not None:
+            line["scaling_detail"] = scaling_detail
+        if check is not None:
+            line["multi_gpu_check"] = check
+        if world == 1 and not args.no_extras:
+            for key, fn in (("kernels", lambda: kernel_table(rt, torch, stream, dev, peaks)), ("prefill", lambda: prefill_gemm(rt, torch, stream, dev, peaks))):
+                try:  # the extra legs never take the measurement down with them
+                    line[key] = fn()
+                except Exception as exc:
+                    line[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
             try:
-                ref_kernel = reference_cuda_kernel(m)
-            except Exception as exc:  # the baseline leg must never take the measurement down with it
-                ref_kernel = None
-                cpu["reference_cuda_kernel_error"] = f"{type(exc).__name__}: {exc}"[:200]
-            if ref_kernel is not None:
-                ref_kernel["this_kernel_speedup"] = ref_kernel["us_per_launch"] / (dom_ms * 1e3)
-                cpu["reference_cuda_kernel"] = ref_kernel
-            line["cpu_baseline"] = cpu
+                line["reference_cuda_kernel"] = reference_cuda_kernels(torch, dev, line["kernels"] if isinstance(line.get("kernels"), list) else [])
+            except Exception as exc:
+                line["reference_cuda_kernel"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        if world == 1 and args.cpu_seconds > 0:
+            line["cpu_baseline"] = cpu_baseline(m, args.cpu_seconds)
         print(json.dumps(line))
     torch.cuda.synchronize()
+    ok = check is None or bool(check.get("ok"))
     rt.set_stream(None)
     rt.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        sys.exit(3)
+
+
+def multi_gpu_check(torch, dist, rt, stream, dev, m, rank, world, launches_of_pass, kind_of, kind_rows, widest, slice_rows, y_local, gathered,
+                    push_launch, combined_ids) -> dict:
+    """One CHAINED layer after the timed regions: every consumer reads the gathered vector that the pushes of its
+    producer left in this rank's exchange region (down from the local activations, then q/k/v <- down, o <- q,
+    gate/up <- o, down <- up, LM head <- down; the widths match), so the peer stores, the flags and the bounded waits
+    are what the data goes through.  Run twice: launch by launch with a barrier in between, then back to back with no
+    host synchronisation at all (the ranks' kernels really wait for one another).  On every rank, after each: (a) each
+    gathered vector equals an NCCL all-gather of the ranks' local slices bit for bit, (b) the combined argmax ids equal
+    the argmax (lowest index on ties) of the all-gathered logits."""
+    chain_input = {"attn_q": "g.ffn_down", "attn_k": "g.ffn_down", "attn_v": "g.ffn_down", "attn_o": "g.attn_q", "ffn_gate": "g.attn_o",
+                   "ffn_up": "g.attn_o", "ffn_down": "g.ffn_up", "output": "g.ffn_down"}
+    n = len(launches_of_pass)
+    layer0 = [i for i in range(n) if launches_of_pass[i][0][0].startswith("blk.0.")]
+    down = next(i for i in layer0 if kind_of(launches_of_pass[i][0][0]) == "ffn_down")
+    order = [(down, False)] + [(i, True) for i in layer0] + [(n - 1, True)]  # (launch, input from the exchange region)
+
+    def gathered_reference(kind: str):
+        """[M][rows] assembled from an NCCL all-gather of the ranks' local [M][slice] blocks."""
+        with torch.cuda.stream(stream):
+            dist.all_gather_into_tensor(gathered[kind], y_local[kind])
+        stream.synchronize()
+        parts = gathered[kind].view(world, -1)
+        return torch.cat([parts[k][: m * slice_rows(kind_rows[kind], k)].view(m, -1) for k in range(world)], dim=1).contiguous()
+
+    def region_vector(kind: str):
+        addr, count = rt.buffer_ptr(f"g.{kind}")
+        got = torch.empty(count, dtype=torch.float32, device=dev)
+        rt.bind("check.tmp", got.data_ptr(), count)
+        rt.copy("check.tmp", 0, f"g.{kind}", 0, count)
+        rt.synchronize()
+        rt.release("check.tmp")
+        return got.view(m, -1)
+
+    def verify(label: str, mismatches: list) -> None:
+        for kind in kind_rows:
+            ref = gathered_reference(kind)
+            if not torch.equal(region_vector(kind).view(torch.int32), ref.view(torch.int32)):
+                mismatches.append(f"{label}: the pushed {kind} vector differs from the all-gather of the slices")
+            if not torch.isfinite(ref).all():
+                mismatches.append(f"{label}: non-finite {kind} outputs")
+        ids = [int(v) for v in combined_ids()]
+        want = [int(v) for v in torch.argmax(gathered_reference("output"), dim=1).tolist()]
+        if ids != want:
+            mismatches.append(f"{label}: combined argmax {ids} != argmax of the gathered logits {want}")
+
+    mismatches: list[str] = []
+    for label, stepwise in (("launch by launch", True), ("back to back", False)):
+        for i, chained in order:
+            push_launch(i, chain_input if chained else None)
+            if stepwise:
+                rt.synchronize()
+                dist.barrier()
+        rt.synchronize()
+        dist.barrier()
+        verify(label, mismatches)
+        dist.barrier()
+    flag = torch.tensor([len(mismatches)], dtype=torch.int64, device=dev)
+    dist.all_reduce(flag)
+    return {"ok": int(flag.item()) == 0, "n_ranks": world, "launches_chained": len(order), "this_rank_mismatches": mismatches[:4],
+            "what": "a chained layer + LM head through the exchange regions, launch by launch and then back to back without host synchronisation: "
+                    "pushed vectors == NCCL all-gather of the slices (bitwise) on every rank; combined argmax ids == argmax of the all-gathered logits"}
 
 
 def main() -> None:
@@ -543,6 +809,7 @@ def main() -> None:
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
                     help="multi-GPU: how output slices are combined - fused peer-memory push from the kernel (default) or NCCL all-gather")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline leg (0 = skip)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel table, the prompt GEMM and the reference's CUDA kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
