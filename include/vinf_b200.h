@@ -150,7 +150,10 @@ int vqm_launch_count(vqm_runtime *rt, uint64_t *out);
 /* Stateless entry point for callers that own all memory: y = W x on `stream` (a cudaStream_t, NULL = legacy
  * default).  w: raw blocks, 16-byte aligned and readable 16 bytes past the end; x: [ntok][cols], y:
  * [ntok][rows], 16-byte aligned fp32; codebook: device copy of the type's codebook or NULL; status: device
- * word that receives a non-zero code if a bounded wait expires (may not be NULL).  1 <= ntok <= 8. */
+ * word that receives a non-zero code if a bounded wait expires (may not be NULL).  1 <= ntok <= 8.
+ * One device per process and one host thread at a time: the launch configuration of a kernel is cached per process, so
+ * a call with another device current than the one this process launched on first returns VQM_ERR_VALUE (this holds for
+ * vqm_runtime_create too). */
 int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
                 unsigned *status, void *stream);
 
@@ -213,10 +216,14 @@ int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const
  * process exits).  It calls no cudaMalloc / cudaFree and no allocating library routine.
  * Limits: 1 <= ntok <= 8 activation rows (more are refused with VQM_ERR_VALUE; split a wider pass into groups
  * of 8 yourself); the launch is capped at 1024 blocks, which is what the array has partial-result slots for.
- * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
- * current); make that first call before any stream capture.  All calls share the one array, which keeps what the
- * last call left in it (the entry point re-zeroes the counter it needs); two calls that overlap on the GPU -
- * different streams, or different host threads - race on it and give undefined results. */
+ * The first call looks up the array's device address (cudaGetSymbolAddress, with the device current), and the first
+ * call for each (type, ntok, shape class) configures its kernel (cudaFuncSetAttribute and an occupancy query, neither
+ * of which allocates device memory): make one warm-up call per shape you will use before any stream capture and
+ * before entering a region that forbids driver set-up work.  The caller zeroes *status before its first call; the
+ * kernel only ever writes a non-zero code to it.  All calls share the one array, which keeps what the last call left in
+ * it (the entry point re-zeroes the counter it needs); two calls that overlap on the GPU - different streams, or
+ * different host threads - race on it and give undefined results.  Like vqm_qmv_raw it serves the one device this
+ * process launched on first (VQM_ERR_VALUE with another device current). */
 int vqm_qmv_argmax_static(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
                           int *out_ids, float *out_values, unsigned *status, void *stream);
 

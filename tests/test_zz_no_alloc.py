@@ -51,6 +51,14 @@ def test_static_scratch_entry_matches_the_regular_fused_argmax_twice(codebooks):
         assert got_vals == want_vals
         assert np.array_equal(rt.read_array("y_new", ntok * rows).view(np.uint32), rt.read_array("y_ref", ntok * rows).view(np.uint32))
         assert np.frombuffer(rt.read("status"), dtype=np.uint32)[0] == 0
+    # the property the entry point exists for: a call (here the ids-only form, y = NULL) leaves the device's free memory as it was
+    free_before = rt.mem_info()[0]
+    rc = lib.vqm_qmv_argmax_static(int(T.Q6_K), ctypes.c_void_p(w_addr), rows, cols, ctypes.c_void_p(ptr["x"]), None, ntok, None,
+                                   ctypes.c_void_p(ptr["ids"]), None, ctypes.c_void_p(ptr["status"]), ctypes.c_void_p(rt.stream()))
+    _capi.check(rc)
+    rt.synchronize()
+    assert rt.mem_info()[0] == free_before
+    assert np.frombuffer(rt.read("ids"), dtype=np.int32)[:ntok].tolist() == want_ids
     # sizes beyond the maximum are refused with a clear error, nothing is launched
     rc = lib.vqm_qmv_argmax_static(int(T.Q6_K), ctypes.c_void_p(w_addr), rows, cols, ctypes.c_void_p(ptr["x"]), None, 9, None,
                                    ctypes.c_void_p(ptr["ids"]), None, ctypes.c_void_p(ptr["status"]), ctypes.c_void_p(rt.stream()))

@@ -56,6 +56,7 @@ struct Buffer {
 struct Graph {
     cudaGraphExec_t exec = nullptr;
     uint64_t kernels = 0;
+    bool uses_gemm_x = false;  // captured a prompt-pass GEMM, i.e. the address of the runtime's fp16 activation buffer
 };
 
 const char *const kCodebookNames[5] = {"iq2xxs_grid", "iq2xs_grid", "iq2s_grid", "iq3xxs_grid", "iq3s_grid"};
@@ -94,6 +95,7 @@ struct vqm_runtime {
     int overlap_launch = 1;  // programmatic dependent launch of consecutive matvecs (VINF_B200_NO_PDL=1 turns it off)
     bool capturing = false;
     uint64_t launches = 0, capture_launches = 0;
+    bool capture_uses_gemm_x = false;
     std::vector<Graph> graphs;
 };
 
@@ -145,6 +147,26 @@ void release(Tensor &t) {
 void release(Buffer &b) {
     if (b.owned && b.data != nullptr) cudaFree(b.data);
     b.data = nullptr;
+}
+
+// The launchers cache what they learn about a kernel (its shared-memory attribute, the blocks per SM) once per process, so
+// every launch of a process has to go to the device the first one went to.  Returns VQM_OK or the error.
+int check_one_device(int *dev_out, int *sm_count_out) {
+    static int first_dev = -1, first_sm_count = 0;
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail("cudaGetDevice", err);
+    if (first_dev < 0) {
+        err = cudaDeviceGetAttribute(&first_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return cuda_fail("device query", err);
+        first_dev = dev;
+    }
+    if (dev != first_dev)
+        return fail(VQM_ERR_VALUE, "this process has launched on device %d before; the library serves one device per process (current device: %d)",
+                    first_dev, dev);
+    if (dev_out != nullptr) *dev_out = dev;
+    if (sm_count_out != nullptr) *sm_count_out = first_sm_count;
+    return VQM_OK;
 }
 
 int no_capture(vqm_runtime *rt, const char *what) {
@@ -279,8 +301,12 @@ int vqm_runtime_create(const void *iq3s_grid, size_t nbytes, vqm_runtime **out) 
     if (iq3s_grid != nullptr && nbytes != 2048)
         return fail(VQM_ERR_VALUE, "iq3s_grid must be 2048 bytes (512 entries x 4 values)");
     vqm_runtime *rt = new vqm_runtime();
-    cudaError_t err = cudaGetDevice(&rt->device);
-    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&rt->sm_count, cudaDevAttrMultiProcessorCount, rt->device);
+    const int dev_rc = check_one_device(&rt->device, &rt->sm_count);
+    if (dev_rc != VQM_OK) {
+        delete rt;
+        return dev_rc;
+    }
+    cudaError_t err = cudaSuccess;
     if (err == cudaSuccess) err = cudaStreamCreate(&rt->own_stream);
     rt->stream = rt->own_stream;
     if (err == cudaSuccess) err = cudaMalloc(&rt->status, 256);
@@ -604,6 +630,11 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
         cudaError_t err = cudaSuccess;
         if (need > rt->gemm_x_len) {
             if ((rc = no_capture(rt, "growing the prompt-pass activation buffer")) != VQM_OK) return rc;
+            // a live graph that captured a prompt pass holds the old buffer's address: it must be destroyed first
+            for (const Graph &g : rt->graphs)
+                if (g.exec != nullptr && g.uses_gemm_x)
+                    return fail(VQM_ERR_VALUE, "a captured graph uses the prompt-pass activation buffer, which a pass of %d rows would have to "
+                                               "grow: destroy that graph first (or run the widest prompt pass once before capturing)", ntok);
             cudaStreamSynchronize(rt->stream);
             cudaFree(rt->gemm_x);
             rt->gemm_x = nullptr;
@@ -621,6 +652,7 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
                 err = vqm::launch_qgemm(t->type, t->data, rt->gemm_x, yp, t->rows, t->cols, static_cast<long long>(t->row_bytes), ntok, cb, rt->stream);
         }
         if (err != cudaSuccess) return cuda_fail("qmv gemm launch", err);
+        if (rt->capturing) rt->capture_uses_gemm_x = true;
         count_launch(rt, 2);
         return VQM_OK;
     }
@@ -790,6 +822,7 @@ int vqm_capture_begin(vqm_runtime *rt) {
     if (err != cudaSuccess) return cuda_fail("cudaStreamBeginCapture", err);
     rt->capturing = true;
     rt->capture_launches = 0;
+    rt->capture_uses_gemm_x = false;
     return VQM_OK;
 }
 
@@ -804,6 +837,7 @@ int vqm_capture_end(vqm_runtime *rt, int *graph_id) {
     cudaGraphDestroy(graph);
     if (err != cudaSuccess) return cuda_fail("cudaGraphInstantiate", err);
     g.kernels = rt->capture_launches;
+    g.uses_gemm_x = rt->capture_uses_gemm_x;
     rt->graphs.push_back(g);
     *graph_id = static_cast<int>(rt->graphs.size()) - 1;
     return VQM_OK;
@@ -965,13 +999,9 @@ int vqm_qmv_raw(int type, const void *w, int rows, int cols, const float *x, flo
     if (((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) != 0)
         return fail(VQM_ERR_VALUE, "w, x and y must be 16-byte aligned");
     if (vqm::grid_is_codebook(type) && codebook == nullptr) return fail(VQM_ERR_VALUE, "GGUF type %d needs its codebook", type);
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaError_t err = cudaGetDevice(&dev);
-        if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (err != cudaSuccess) return cuda_fail("device query", err);
-    }
+    int sm_count = 0;
+    const int dev_rc = check_one_device(nullptr, &sm_count);
+    if (dev_rc != VQM_OK) return dev_rc;
     vqm::MatvecArgs a{};
     set_single_part(a, static_cast<const uint8_t *>(w), y, rows);
     a.x = x;
@@ -1014,22 +1044,17 @@ int vqm_qmv_argmax_static(int type, const void *w, int rows, int cols, const flo
     if (vqm::grid_is_codebook(type) && codebook == nullptr) return fail(VQM_ERR_VALUE, "GGUF type %d needs its codebook", type);
     // Set-up, once per device and with that device current: the array's name is only a host-side handle, the kernel
     // needs the device address behind it.
-    static StaticArgmaxScratch *scratch_of_device[64] = {};
-    static int sm_count_of_device[64] = {};
-    int dev = 0;
-    cudaError_t err = cudaGetDevice(&dev);
-    if (err != cudaSuccess) return cuda_fail("cudaGetDevice", err);
-    if (dev < 0 || dev >= 64) return fail(VQM_ERR_VALUE, "device ordinal %d is not supported", dev);
-    if (scratch_of_device[dev] == nullptr) {
+    static StaticArgmaxScratch *scratch = nullptr;  // (one device per process, see check_one_device)
+    int dev = 0, sm_count = 0;
+    const int dev_rc = check_one_device(&dev, &sm_count);
+    if (dev_rc != VQM_OK) return dev_rc;
+    cudaError_t err = cudaSuccess;
+    if (scratch == nullptr) {
         void *ptr = nullptr;
         err = cudaGetSymbolAddress(&ptr, g_static_argmax_scratch);
         if (err != cudaSuccess) return cuda_fail("cudaGetSymbolAddress", err);
-        err = cudaDeviceGetAttribute(&sm_count_of_device[dev], cudaDevAttrMultiProcessorCount, dev);
-        if (err != cudaSuccess) return cuda_fail("device query", err);
-        scratch_of_device[dev] = static_cast<StaticArgmaxScratch *>(ptr);
+        scratch = static_cast<StaticArgmaxScratch *>(ptr);
     }
-    StaticArgmaxScratch *scratch = scratch_of_device[dev];
-    const int sm_count = sm_count_of_device[dev];
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // The counter must start at zero; an earlier call that was cut short could have left it otherwise.
     err = cudaMemsetAsync(&scratch->done_counter, 0, sizeof(unsigned), st);
