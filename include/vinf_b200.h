@@ -80,6 +80,14 @@ int vqm_alloc(vqm_runtime *rt, const char *name, size_t n, int elem);
 /* Registers caller-owned device memory under a buffer name (the runtime will not free it).  Lets a second
  * runtime or a torch tensor share memory, the use the reference makes of buffer_ptr (qwen_runtime.cu:1473-1483). */
 int vqm_bind(vqm_runtime *rt, const char *name, void *device_ptr, size_t n, int elem);
+/* Weights straight from a file: `nbytes` raw block bytes at byte `offset` of `path` (for a GGUF file: the tensor's
+ * absolute offset) become the resident tensor `name`, without passing through a caller buffer.  Replaces the reference's
+ * mmap + blocking upload per tensor (engine/src/vinf/cuda/qwen_runtime.py:68-86 over GGUFFile.mmap_tensor,
+ * engine/src/vinf/gguf/parser.py:153-159).  `threads` (1..16, 0 = 4) readers pread 8 MiB chunks into pinned staging and
+ * copy them to the device on their own streams, so reading and copying overlap.  Synchronous; same shape checks and
+ * errors as vqm_upload, plus VQM_ERR_VALUE when the file cannot be opened, is too short or a read fails. */
+int vqm_upload_file(vqm_runtime *rt, const char *name, const char *path, uint64_t offset, uint64_t nbytes, int type, int cols, int rows,
+                    int threads);
 /* Same for a weight tensor that already sits in device memory (e.g. a row shard of a larger tensor). */
 int vqm_bind_tensor(vqm_runtime *rt, const char *name, const void *device_ptr, int type, int cols, int rows);
 int vqm_release(vqm_runtime *rt, const char *buffer_name);
@@ -112,6 +120,18 @@ int vqm_argmax_rows(vqm_runtime *rt, const char *x, int n, int ntok, int *out);
  * ntok <= 8.  out_ids (host, ntok ints) may be NULL: then the call is asynchronous and the ids stay in
  * the device buffer returned by vqm_argmax_result(). */
 int vqm_qmv_argmax(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int *out_ids);
+/* The matvec with the prologues and epilogues of the reference's fused QMV instruction (flags and meaning:
+ * engine/csrc/common/qwen_mk_abi.h:55-58, engine/csrc/megakernel/qwen_megakernel.cu:486-550 and :231), so that the
+ * element-wise kernels around a matvec need no launch of their own:
+ *   VQM_FUSE_SILU_MUL  the activations are silu(x) * x2 (the FFN's down projection reads gate and up directly);
+ *   VQM_FUSE_NORM      then v * rsqrt(mean(v^2) + eps) * norm_weight over the columns of each activation row
+ *                      (norm_weight: an fp32 buffer of `cols` values, or an F32 tensor with `cols` elements);
+ *   VQM_FUSE_ADD       y += W v instead of y = W v (y already holds the residual);
+ *   VQM_FUSE_ARGMAX    the fused argmax of vqm_qmv_argmax over the stored values (after the residual); out_ids as there.
+ * 1 <= ntok <= 8; every activation row is transformed on its own.  x and x2 are not modified. */
+enum { VQM_FUSE_ADD = 1, VQM_FUSE_NORM = 2, VQM_FUSE_ARGMAX = 4, VQM_FUSE_SILU_MUL = 8 };
+int vqm_qmv_fused(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int flags, const char *x2,
+                  const char *norm_weight, float eps, int *out_ids);
 /* Device arrays holding the last fused argmax: ids[8] (int32) and values[8] (fp32). */
 int vqm_argmax_result(vqm_runtime *rt, uint64_t *ids_addr, uint64_t *values_addr);
 /* Blocking copy of the first ntok ids (and, if values is not NULL, values) of the last fused argmax to the host. */

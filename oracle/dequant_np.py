@@ -291,3 +291,17 @@ def cpu_qwen_bound(raw, tensor_type: int, rows: int, cols: int, x: np.ndarray,
     w = np.abs(dequantize(raw, tensor_type, rows * cols, codebooks)).reshape(rows, cols // 32, 32).sum(axis=2)
     amax = np.abs(x2).reshape(x2.shape[0], cols // 32, 32).max(axis=2)
     return 1.05 * (amax / 254.0) @ w.T
+
+
+def fused_matvec(raw, tensor_type: int, rows: int, cols: int, x, codebooks=None, *, x2=None, norm_w=None, eps: float = 1e-6, residual=None):
+    """y = W v (+ residual) in double precision with the activation prologues of the reference's fused QMV instruction
+    (engine/csrc/megakernel/qwen_megakernel.cu:486-550): v = silu(x) * x2 if x2 is given, else x; with norm_w,
+    v * rsqrt(mean(v^2) + eps) * norm_w per activation row; `:231`: the result is added to what y held.  Test infrastructure."""
+    v = np.atleast_2d(np.asarray(x, dtype=np.float64))
+    if x2 is not None:
+        v = v / (1.0 + np.exp(-v)) * np.atleast_2d(np.asarray(x2, dtype=np.float64))
+    if norm_w is not None:
+        v = v / np.sqrt(np.mean(v * v, axis=1, keepdims=True) + eps) * np.asarray(norm_w, dtype=np.float64)[None, :]
+    w = dequantize(raw, tensor_type, rows * cols, codebooks).reshape(rows, cols)
+    y = v @ w.T
+    return y if residual is None else y + np.asarray(residual, dtype=np.float64)

@@ -513,3 +513,29 @@ def test_qmv_real_model_shapes(rt, clib, codebooks, t, rows, cols, ntok):
     got = run_qmv(rt, raw, t, rows, cols, x)
     ref = oracle_libs.c_qmv(clib, raw, int(t), rows, cols, x, codebooks)
     assert rel_l2(got, ref) <= REL_L2
+
+
+def test_a_graph_that_captured_a_prompt_pass_pins_the_activation_buffer(rt, codebooks):
+    """A captured prompt pass holds the address of the runtime's fp16 activation buffer: a wider pass that would have to
+    replace that buffer is refused until the graph is destroyed."""
+    rng = np.random.default_rng(77)
+    rows, cols = 96, 8192  # 1024 x 8192 activations: more than any earlier prompt pass of this module has sized the buffer for
+    rt.upload("w", synthetic_blocks(T.Q4_K, rows, cols, rng), int(T.Q4_K), cols, rows)
+    rt.alloc("x", 1024 * cols)
+    rt.alloc("y", 1024 * rows)
+    rt.set_gemm_min_rows(64)
+    try:
+        rt.qmv("w", "x", "y", 64)  # sizes the buffer for 64 rows
+        rt.synchronize()
+        rt.capture_begin()
+        rt.qmv("w", "x", "y", 64)
+        graph = rt.capture_end()
+        with pytest.raises(ValueError, match="captured graph"):
+            rt.qmv("w", "x", "y", 1024)
+        rt.graph_launch(graph)  # still valid
+        rt.synchronize()
+        rt.graph_destroy(graph)
+        rt.qmv("w", "x", "y", 1024)  # now the buffer may grow
+        rt.synchronize()
+    finally:
+        rt.set_gemm_min_rows(0)

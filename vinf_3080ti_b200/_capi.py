@@ -32,6 +32,7 @@ SIGNATURES: dict[str, list] = {
     "vqm_runtime_destroy": [c_void_p],
     "vqm_set_codebook": [c_void_p, c_char_p, c_void_p, c_size_t],
     "vqm_upload": [c_void_p, c_char_p, c_void_p, c_size_t, c_int, c_int, c_int],
+    "vqm_upload_file": [c_void_p, c_char_p, c_char_p, c_uint64, c_uint64, c_int, c_int, c_int, c_int],
     "vqm_free": [c_void_p, c_char_p],
     "vqm_has": [c_void_p, c_char_p, POINTER(c_int)],
     "vqm_device_bytes": [c_void_p, POINTER(c_size_t)],
@@ -54,6 +55,7 @@ SIGNATURES: dict[str, list] = {
     "vqm_argmax": [c_void_p, c_char_p, c_int, POINTER(c_int)],
     "vqm_argmax_rows": [c_void_p, c_char_p, c_int, c_int, POINTER(c_int)],
     "vqm_qmv_argmax": [c_void_p, c_char_p, c_char_p, c_char_p, c_int, POINTER(c_int)],
+    "vqm_qmv_fused": [c_void_p, c_char_p, c_char_p, c_char_p, c_int, c_int, c_char_p, c_char_p, ctypes.c_float, POINTER(c_int)],
     "vqm_argmax_result": [c_void_p, POINTER(c_uint64), POINTER(c_uint64)],
     "vqm_argmax_fetch": [c_void_p, c_int, POINTER(c_int), POINTER(ctypes.c_float)],
     "vqm_set_argmax_row_base": [c_void_p, c_char_p, c_int],

@@ -2,7 +2,7 @@
 
     python -m vinf_3080ti_b200.build [--force] [--jobs N]
 
-One translation unit per GGUF type (the matvec kernel instantiations) plus the small kernels and the
+Two translation units per GGUF type (the matvec kernel instantiations, plain and with the fused prologues) plus the small kernels and the
 runtime; objects go to csrc/build/, the library next to this file.  Cross-compiles without a GPU.
 """
 from __future__ import annotations
@@ -67,6 +67,9 @@ def build(force: bool = False, jobs: int | None = None, verbose: bool = False) -
         ("vqm_matvec_type.cu", [f"-DVQM_TYPE={tid}", f"-DVQM_TYPE_NAME={tname}"], OBJ / f"matvec_{tname}.o")
         for tid, tname in TYPES
     ]
+    # the same kernels with the fused prologues / residual add compiled in (vqm_qmv_fused)
+    work += [("vqm_matvec_type.cu", [f"-DVQM_TYPE={tid}", f"-DVQM_TYPE_NAME={tname}", "-DVQM_FUSED=1"], OBJ / f"matvec_fused_{tname}.o")
+             for tid, tname in TYPES]
     work.append(("vqm_aux.cu", [], OBJ / "aux.o"))
     work.append(("vqm_gemm.cu", [], OBJ / "gemm.o"))
     work.append(("vqm_gemm_tc5.cu", [], OBJ / "gemm_tc5.o"))

@@ -54,8 +54,17 @@ struct MatvecArgs {
     int allow_split;         // host only: the caller permits the split
     int overlap_launch;      // host only: launch with programmatic stream serialization (see qmv_kernel)
     int max_grid;            // host only: upper bound on the grid (0 = none); sizes the argmax partial arrays
+    // Fused prologue / epilogue (the flags of the reference's megakernel QMV, engine/csrc/common/qwen_mk_abi.h:55-58):
+    //   kFuseSiluMul: the activations are silu(x) * x2;  kFuseNorm: then rmsnorm over the columns times norm_w;
+    //   kFuseAdd: y += W x instead of y = W x (the outputs already hold the residual).
+    int fuse;                // kFuse* bits, 0 = plain matvec
+    const float *x2;         // [M][cols], with kFuseSiluMul
+    const float *norm_w;     // [cols], with kFuseNorm
+    float eps;               // rmsnorm epsilon
     PushInfo push;           // all zero when the tensor is not sharded
 };
+
+enum : int { kFuseAdd = 1, kFuseNorm = 2, kFuseSiluMul = 8 };  // (4 is the fused argmax, which has its own fields)
 
 constexpr int kMaxSplit = 8;  // column ranges a row can be split into (the portable cluster size)
 
@@ -66,8 +75,9 @@ enum : unsigned { kStatusOk = 0, kStatusWaitExpired = 1, kStatusPeerWaitExpired 
 #define VQM_FOR_EACH_TYPE(X) \
     X(0, F32) X(1, F16) X(8, Q8_0) X(10, Q2_K) X(11, Q3_K) X(12, Q4_K) X(13, Q5_K) X(14, Q6_K) X(16, IQ2_XXS) \
     X(17, IQ2_XS) X(18, IQ3_XXS) X(20, IQ4_NL) X(21, IQ3_S) X(22, IQ2_S) X(23, IQ4_XS)
-#define VQM_DECLARE_LAUNCHER(id, name) \
-    cudaError_t launch_qmv_##name(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out);
+#define VQM_DECLARE_LAUNCHER(id, name)                                                                            \
+    cudaError_t launch_qmv_##name(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out); \
+    cudaError_t launch_qmv_fused_##name(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out);  // honours a.fuse
 VQM_FOR_EACH_TYPE(VQM_DECLARE_LAUNCHER)
 #undef VQM_DECLARE_LAUNCHER
 

@@ -46,6 +46,12 @@ namespace vqm {
 constexpr int kWarps = 8;                      // warps per block
 constexpr int kMaxTok = 8;                     // activation rows per launch
 constexpr int kBarrierBytes = 1024;            // mbarriers and counters at the front of shared memory
+// The kernels with the fused prologues and the residual add are separate instantiations (a second set of translation
+// units, -DVQM_FUSED=1), so that the plain matvec carries none of their code.
+#ifndef VQM_FUSED
+#define VQM_FUSED 0
+#endif
+constexpr bool kFusedBuild = VQM_FUSED != 0;
 
 __host__ __device__ constexpr int table_bytes_padded(int type) { return (grid_bytes(type) + 15) / 16 * 16; }
 
@@ -201,7 +207,9 @@ __device__ __forceinline__ uintptr_t row_address(const MatvecArgs &a, int g) {
 
 // ---- the kernel ------------------------------------------------------------------------------------------
 
-template <int TYPE, int M, int RW>
+// FUSED: with the activation prologues and the residual add compiled in (kFusedBuild of the translation unit; a template
+// parameter so that the two builds of a kernel are two different functions).
+template <int TYPE, int M, int RW, bool FUSED>
 __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel(const MatvecArgs a) {
     using StepT = Step<TYPE, M, RW>;
     constexpr int S = w_stages<TYPE, M, RW>();
@@ -212,7 +220,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     constexpr int XSTAGE = M * kSegCols * 4;
     constexpr bool kAligned = block_align(TYPE) >= 16;  // every segment starts on a 16-byte boundary
     static_assert(RW * M <= 32, "one lane per (row, activation row) output");
-    static_assert(kWarps * 8 * 8 + 8 * 8 + 8 * 4 <= kBarrierBytes, "barrier area");
+    static_assert(kWarps * 8 * 8 + 8 * 8 + 8 * 4 + 8 * 8 + kMaxTok * 4 <= kBarrierBytes, "barrier area");
 
     __shared__ float s_split[kMaxSplit][kWarps][kMaxTok];  // column split: partial sums of the cluster's blocks (first block's copy)
     extern __shared__ __align__(128) uint8_t smem[];
@@ -223,6 +231,8 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
     uint8_t *table = smem;
     int *xdone = reinterpret_cast<int *>(smem + TABLE + (kWarps * 8 + 8) * 8);
     const uint32_t xfull = smem0 + TABLE + kWarps * 8 * 8;
+    const uint32_t xready = xfull + 8 * 8 + 8 * 4;  // fused prologue: "every thread has transformed its share of the stage"
+    float *norm_scale = reinterpret_cast<float *>(smem + TABLE + (kWarps * 8 + 8) * 8 + 8 * 4 + 8 * 8);  // [kMaxTok]
     const uint32_t xbuf = smem0 + TABLE + kBarrierBytes;
     const uint32_t bar = smem0 + TABLE + warp * 64;
     const uint32_t buf = xbuf + XS * XSTAGE + warp * (S * RW * SLOT);
@@ -236,6 +246,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
 #pragma unroll
         for (int s = 0; s < XS; ++s) {
             mbar_init(xfull + s * 8, 1);
+            mbar_init(xready + s * 8, kWarps * 32);
             xdone[s] = 0;
         }
     }
@@ -367,6 +378,34 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
         __syncthreads();
     }
 
+    // Fused prologue (engine/csrc/megakernel/qwen_megakernel.cu:486-550): v = silu(x) * x2 or x, then with rmsnorm
+    // v * rsqrt(mean(v^2) + eps) * norm_w.  Every block computes the M scales over all columns once; the staged
+    // segments are then transformed in place by all threads of the block before anyone reads them.
+    const bool transform = FUSED && (a.fuse & (kFuseNorm | kFuseSiluMul)) != 0;
+    auto activation = [&](int t, int col) {
+        const float v = a.x[static_cast<size_t>(t) * a.cols + col];
+        return (a.fuse & kFuseSiluMul) ? v / (1.0f + expf(-v)) * a.x2[static_cast<size_t>(t) * a.cols + col] : v;
+    };
+    if (FUSED && (a.fuse & kFuseNorm)) {
+        __shared__ float s_part[kWarps];
+        for (int t = 0; t < M; ++t) {
+            float local = 0.0f;
+            for (int col = threadIdx.x; col < a.cols; col += kWarps * 32) {
+                const float v = activation(t, col);
+                local = fmaf(v, v, local);
+            }
+            local = warp_sum(local);
+            if (lane == 0) s_part[warp] = local;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float total = 0.0f;
+                for (int w = 0; w < kWarps; ++w) total += s_part[w];
+                norm_scale[t] = 1.0f / sqrtf(total / static_cast<float>(a.cols) + a.eps);
+            }
+            __syncthreads();
+        }
+    }
+
     f32x2 acc[RW][M];
 #pragma unroll
     for (int r = 0; r < RW; ++r)
@@ -392,6 +431,41 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                 break;
             }
 #endif
+            if (transform) {
+                // this thread's share of the stage: columns 4 * tid .. 4 * tid + 3 of every activation row
+                const int col0 = col_begin + seg * kSegCols, cols_here = seg == n_seg - 1 ? cols_last : kSegCols;
+                const int c = 4 * static_cast<int>(threadIdx.x);
+                if (c < cols_here) {
+#pragma unroll
+                    for (int t = 0; t < M; ++t) {
+                        const uint32_t at = xbuf + xstage * XSTAGE + (t * kSegCols + c) * 4;
+                        float v[4];
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(at));
+                        if (a.fuse & kFuseSiluMul) {
+                            const float4 g = *reinterpret_cast<const float4 *>(a.x2 + static_cast<size_t>(t) * a.cols + col0 + c);
+                            v[0] = v[0] / (1.0f + expf(-v[0])) * g.x;
+                            v[1] = v[1] / (1.0f + expf(-v[1])) * g.y;
+                            v[2] = v[2] / (1.0f + expf(-v[2])) * g.z;
+                            v[3] = v[3] / (1.0f + expf(-v[3])) * g.w;
+                        }
+                        if (a.fuse & kFuseNorm) {
+                            const float4 nw = *reinterpret_cast<const float4 *>(a.norm_w + col0 + c);
+                            const float sc = norm_scale[t];
+                            v[0] *= sc * nw.x;
+                            v[1] *= sc * nw.y;
+                            v[2] *= sc * nw.z;
+                            v[3] *= sc * nw.w;
+                        }
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+                    }
+                }
+                // a bounded block-wide rendezvous: everybody has written its share before anybody reads the stage
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(xready + xstage * 8) : "memory");
+                if (!mbar_wait_bounded(xready + xstage * 8, xphase)) {
+                    expired = true;
+                    break;
+                }
+            }
             if (nrows > 0) {
 #ifndef VQM_PURE_COMPUTE
                 if (!mbar_wait_bounded(c_bar, phase)) {
@@ -476,6 +550,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                     } else {
                         mine *= StepT::kOutScale;  // exact: 1 or a power of two (see bytes_to_subpair)
                         const RowHome h = home_of(a, row);
+                        if (FUSED && (a.fuse & kFuseAdd) && h.y != nullptr) mine += h.y[static_cast<size_t>(t) * h.rows + h.local];  // y += W x
                         if (h.y != nullptr) h.y[static_cast<size_t>(t) * h.rows + h.local] = mine;
                         if (a.push.push_slot > 0) {
                             // row-sharded: the value also goes straight into every rank's gathered [M][rows_total] vector
@@ -512,6 +587,7 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                 for (int k = 0; k < k_split; ++k) sum += s_split[k][w][t];
                 sum *= StepT::kOutScale;
                 const RowHome h = home_of(a, row);
+                if (FUSED && (a.fuse & kFuseAdd) && h.y != nullptr) sum += h.y[static_cast<size_t>(t) * h.rows + h.local];
                 if (h.y != nullptr) h.y[static_cast<size_t>(t) * h.rows + h.local] = sum;
                 if (a.push.push_slot > 0) {
                     const size_t at = static_cast<size_t>(t) * h.rows_total + h.row_begin + h.local;

@@ -24,10 +24,10 @@ struct Variant {
         if (cached >= 0) return cached;
         cached = 0;
         if constexpr (kFits) {
-            if (cudaFuncSetAttribute(qmv_kernel<VQM_TYPE, M, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            if (cudaFuncSetAttribute(qmv_kernel<VQM_TYPE, M, RW, kFusedBuild>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(kSmem)) == cudaSuccess) {
                 int n = 0;
-                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, qmv_kernel<VQM_TYPE, M, RW>, kWarps * 32, kSmem) == cudaSuccess)
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, qmv_kernel<VQM_TYPE, M, RW, kFusedBuild>, kWarps * 32, kSmem) == cudaSuccess)
                     cached = n;
             }
             (void)cudaGetLastError();
@@ -76,7 +76,7 @@ struct Variant {
             }
             cfg.attrs = attr;
             cfg.numAttrs = n_attr;
-            return cudaLaunchKernelEx(&cfg, qmv_kernel<VQM_TYPE, M, RW>, a);
+            return cudaLaunchKernelEx(&cfg, qmv_kernel<VQM_TYPE, M, RW, kFusedBuild>, a);
         } else {
             return cudaErrorInvalidConfiguration;
         }
@@ -126,7 +126,13 @@ cudaError_t launch_one(const MatvecArgs &args, int sm_count, cudaStream_t stream
 #define VQM_CAT2(a, b) a##b
 #define VQM_CAT(a, b) VQM_CAT2(a, b)
 
-cudaError_t VQM_CAT(launch_qmv_, VQM_TYPE_NAME)(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out) {
+#if VQM_FUSED
+#define VQM_LAUNCHER_PREFIX launch_qmv_fused_
+#else
+#define VQM_LAUNCHER_PREFIX launch_qmv_
+#endif
+
+cudaError_t VQM_CAT(VQM_LAUNCHER_PREFIX, VQM_TYPE_NAME)(const MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid_out) {
     switch (m) {
         case 1: return launch_one<1>(a, sm_count, stream, grid_out);
         case 2: return launch_one<2>(a, sm_count, stream, grid_out);

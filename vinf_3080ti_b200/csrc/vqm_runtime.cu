@@ -4,13 +4,18 @@
 // for the lookups and their errors, :1338-1409 upload, :1616-1650 alloc, :1819-1912 write/read/qmv,
 // :2167-2197 argmax, :2281-2315 matvec).  Weights are always resident: there is no host ring or VMM group.
 #include <cuda_runtime.h>
+#include <fcntl.h>
+#include <unistd.h>
 
+#include <atomic>
+#include <cerrno>
 #include <climits>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -97,6 +102,10 @@ struct vqm_runtime {
     uint64_t launches = 0, capture_launches = 0;
     bool capture_uses_gemm_x = false;
     std::vector<Graph> graphs;
+    // file loader: per reader thread two pinned staging slots, a copy stream and an event per slot (created on first use)
+    std::vector<uint8_t *> load_slots;
+    std::vector<cudaStream_t> load_streams;
+    std::vector<cudaEvent_t> load_events;
 };
 
 namespace {
@@ -182,7 +191,7 @@ void count_launch(vqm_runtime *rt, uint64_t n = 1) {
 cudaError_t dispatch_qmv(int type, const vqm::MatvecArgs &a, int m, int sm_count, cudaStream_t stream, int *grid) {
     switch (type) {
 #define VQM_CASE(id, name) \
-    case id: return vqm::launch_qmv_##name(a, m, sm_count, stream, grid);
+    case id: return a.fuse != 0 ? vqm::launch_qmv_fused_##name(a, m, sm_count, stream, grid) : vqm::launch_qmv_##name(a, m, sm_count, stream, grid);
         VQM_FOR_EACH_TYPE(VQM_CASE)
 #undef VQM_CASE
         default: return cudaErrorInvalidValue;
@@ -207,8 +216,14 @@ void set_single_part(vqm::MatvecArgs &a, const uint8_t *w, float *y, int rows) {
 
 // Launches y_p = W_p x for the n tensors of a group (same type and columns; one launch) and m <= 8 rows of x,
 // optionally with the fused argmax (n = 1 only).
+struct Fuse {
+    int flags = 0;
+    const float *x2 = nullptr, *norm_w = nullptr;
+    float eps = 0.0f;
+};
+
 int launch_parts(vqm_runtime *rt, int n, const Tensor *const *ts, const float *x, float *const *ys, int m, bool with_argmax,
-                 const vqm::PushInfo *push = nullptr) {
+                 const vqm::PushInfo *push = nullptr, const Fuse *fuse = nullptr) {
     const Tensor &t0 = *ts[0];
     const uint8_t *cb = codebook_for(rt, t0.type);
     if (vqm::grid_is_codebook(t0.type) && cb == nullptr)
@@ -237,6 +252,12 @@ int launch_parts(vqm_runtime *rt, int n, const Tensor *const *ts, const float *x
     if (push != nullptr) {
         a.push = *push;
         a.done_counter = rt->done_counter;
+    }
+    if (fuse != nullptr) {
+        a.fuse = fuse->flags;
+        a.x2 = fuse->x2;
+        a.norm_w = fuse->norm_w;
+        a.eps = fuse->eps;
     }
     if (with_argmax) {
         a.part_val = rt->part_val;
@@ -354,6 +375,9 @@ void vqm_runtime_destroy(vqm_runtime *rt) {
     cudaFree(rt->gemm_x);
     for (void *p : rt->exchange_opened) cudaIpcCloseMemHandle(p);
     cudaFree(rt->exchange_own);
+    for (uint8_t *p : rt->load_slots) cudaFreeHost(p);
+    for (cudaStream_t st : rt->load_streams) cudaStreamDestroy(st);
+    for (cudaEvent_t ev : rt->load_events) cudaEventDestroy(ev);
     if (rt->stream != nullptr) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -394,6 +418,141 @@ int vqm_upload(vqm_runtime *rt, const char *name, const void *data, size_t nbyte
     if (err != cudaSuccess) {
         release(t);
         return cuda_fail("upload tensor", err);
+    }
+    t.type = type;
+    t.rows = rows;
+    t.cols = cols;
+    t.row_bytes = row_bytes;
+    t.nbytes = want;
+    rt->tensors[name] = t;
+    return VQM_OK;
+}
+
+// Weights straight from a file into HBM (replaces the reference's mmap + one blocking cudaMemcpy per tensor,
+// engine/src/vinf/cuda/qwen_runtime.py:68-86 with engine/src/vinf/gguf/parser.py:153-159, and with it the residency
+// planner: every tensor ends up resident).  `threads` readers take the tensor's 8 MiB chunks in turn; each owns two
+// pinned staging slots and a copy stream, so the pread of one chunk overlaps the host-to-device copy of the previous
+// one and the readers overlap one another.  Synchronous like vqm_upload: on return the bytes are in device memory.
+constexpr size_t kLoadChunk = 8u << 20;
+constexpr int kMaxLoadThreads = 16;
+
+int vqm_upload_file(vqm_runtime *rt, const char *name, const char *path, uint64_t offset, uint64_t nbytes, int type, int cols, int rows,
+                    int threads) {
+    size_t row_bytes = 0;
+    int rc = check_shape(name, type, cols, rows, &row_bytes);
+    if (rc != VQM_OK) return rc;
+    const size_t want = row_bytes * static_cast<size_t>(rows);
+    if (nbytes != want) return fail(VQM_ERR_VALUE, "%s: got %llu bytes, expected %zu", name, static_cast<unsigned long long>(nbytes), want);
+    if (path == nullptr) return fail(VQM_ERR_VALUE, "path must not be NULL");
+    if ((rc = no_capture(rt, "upload_file")) != VQM_OK) return rc;
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(VQM_ERR_VALUE, "%s: cannot open %s: %s", name, path, strerror(errno));
+    const off_t file_size = lseek(fd, 0, SEEK_END);
+    if (file_size < 0 || static_cast<uint64_t>(file_size) < offset + nbytes) {
+        close(fd);
+        return fail(VQM_ERR_VALUE, "%s: %s has %lld bytes, the tensor needs [%llu, %llu)", name, path, static_cast<long long>(file_size),
+                    static_cast<unsigned long long>(offset), static_cast<unsigned long long>(offset + nbytes));
+    }
+    const size_t n_chunks = (want + kLoadChunk - 1) / kLoadChunk;
+    int n_threads = threads <= 0 ? 4 : threads > kMaxLoadThreads ? kMaxLoadThreads : threads;
+    if (static_cast<size_t>(n_threads) > n_chunks) n_threads = static_cast<int>(n_chunks);
+    cudaError_t err = cudaSuccess;
+    while (static_cast<int>(rt->load_streams.size()) < n_threads && err == cudaSuccess) {  // staging for one more reader
+        uint8_t *slots[2] = {nullptr, nullptr};
+        cudaEvent_t events[2] = {nullptr, nullptr};
+        cudaStream_t st = nullptr;
+        for (int i = 0; i < 2 && err == cudaSuccess; ++i) {
+            err = cudaHostAlloc(reinterpret_cast<void **>(&slots[i]), kLoadChunk, cudaHostAllocDefault);
+            if (err == cudaSuccess) err = cudaEventCreateWithFlags(&events[i], cudaEventDisableTiming);
+        }
+        if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+        if (err != cudaSuccess) {
+            for (int i = 0; i < 2; ++i) {
+                if (slots[i] != nullptr) cudaFreeHost(slots[i]);
+                if (events[i] != nullptr) cudaEventDestroy(events[i]);
+            }
+            break;
+        }
+        rt->load_slots.push_back(slots[0]);
+        rt->load_slots.push_back(slots[1]);
+        rt->load_events.push_back(events[0]);
+        rt->load_events.push_back(events[1]);
+        rt->load_streams.push_back(st);
+    }
+    if (err != cudaSuccess) {
+        close(fd);
+        return cuda_fail("file loader staging", err);
+    }
+    auto it = rt->tensors.find(name);
+    if (it != rt->tensors.end()) {
+        cudaStreamSynchronize(rt->stream);
+        release(it->second);
+        rt->tensors.erase(it);
+    }
+    Tensor t;
+    const size_t padded = (want + 16 + 255) / 256 * 256;  // as in vqm_upload
+    err = cudaMalloc(&t.data, padded);
+    if (err == cudaSuccess) err = cudaMemset(t.data + want, 0, padded - want);
+    if (err != cudaSuccess) {
+        close(fd);
+        release(t);
+        return cuda_fail("upload_file", err);
+    }
+    std::atomic<int> first_error{0};  // 0 fine, 1 read error, 2 CUDA error
+    std::string read_error;
+    cudaError_t cuda_error = cudaSuccess;
+    auto reader = [&](int tid) {
+        if (cudaSetDevice(rt->device) != cudaSuccess) {
+            first_error = 2;
+            return;
+        }
+        uint8_t *const *slots = &rt->load_slots[2 * tid];
+        cudaEvent_t *events = &rt->load_events[2 * tid];
+        bool used[2] = {false, false};
+        int turn = 0;
+        for (size_t chunk = static_cast<size_t>(tid); chunk < n_chunks && first_error == 0; chunk += static_cast<size_t>(n_threads), turn ^= 1) {
+            if (used[turn] && cudaEventSynchronize(events[turn]) != cudaSuccess) {  // the slot's previous copy has left it
+                first_error = 2;
+                return;
+            }
+            const size_t at = chunk * kLoadChunk, len = want - at < kLoadChunk ? want - at : kLoadChunk;
+            size_t done = 0;
+            while (done < len) {
+                const ssize_t got = pread(fd, slots[turn] + done, len - done, static_cast<off_t>(offset + at + done));
+                if (got <= 0) {
+                    if (got < 0 && errno == EINTR) continue;
+                    int expected = 0;
+                    if (first_error.compare_exchange_strong(expected, 1)) read_error = got == 0 ? "unexpected end of file" : strerror(errno);
+                    return;
+                }
+                done += static_cast<size_t>(got);
+            }
+            cudaError_t e = cudaMemcpyAsync(t.data + at, slots[turn], len, cudaMemcpyHostToDevice, rt->load_streams[tid]);
+            if (e == cudaSuccess) e = cudaEventRecord(events[turn], rt->load_streams[tid]);
+            if (e != cudaSuccess) {
+                int expected = 0;
+                if (first_error.compare_exchange_strong(expected, 2)) cuda_error = e;
+                return;
+            }
+            used[turn] = true;
+        }
+    };
+    std::vector<std::thread> workers;
+    for (int tid = 1; tid < n_threads; ++tid) workers.emplace_back(reader, tid);
+    reader(0);
+    for (auto &w : workers) w.join();
+    for (int tid = 0; tid < n_threads; ++tid) {
+        const cudaError_t e = cudaStreamSynchronize(rt->load_streams[tid]);
+        if (e != cudaSuccess && first_error == 0) {
+            first_error = 2;
+            cuda_error = e;
+        }
+    }
+    close(fd);
+    if (first_error != 0) {
+        release(t);
+        if (first_error == 1) return fail(VQM_ERR_VALUE, "%s: reading %s failed: %s", name, path, read_error.c_str());
+        return cuda_fail("upload_file copy", cuda_error);
     }
     t.type = type;
     t.rows = rows;
@@ -684,6 +843,59 @@ int vqm_qmv_argmax(vqm_runtime *rt, const char *weight, const char *x, const cha
         cudaError_t err = cudaMemcpyAsync(out_ids, rt->argmax_ids, sizeof(int) * ntok, cudaMemcpyDeviceToHost, rt->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
         if (err != cudaSuccess) return cuda_fail("qmv_argmax", err);
+    }
+    return VQM_OK;
+}
+
+int vqm_qmv_fused(vqm_runtime *rt, const char *weight, const char *x, const char *y, int ntok, int flags, const char *x2, const char *norm_weight,
+                  float eps, int *out_ids) {
+    if (ntok < 1 || ntok > 8) return fail(VQM_ERR_VALUE, "ntok must be in [1, 8] for the fused matvec");
+    if ((flags & ~(VQM_FUSE_ADD | VQM_FUSE_NORM | VQM_FUSE_ARGMAX | VQM_FUSE_SILU_MUL)) != 0) return fail(VQM_ERR_VALUE, "unknown flag bits %d", flags);
+    int rc = VQM_OK;
+    Tensor *t = find_tensor(rt, weight, &rc);
+    if (t == nullptr) return rc;
+    if (t->cols % 32 != 0) return fail(VQM_ERR_VALUE, "%s: matvec cols must be a multiple of 32", weight);
+    const float *xp = find_f32(rt, x, static_cast<size_t>(t->cols) * ntok, &rc);
+    if (xp == nullptr) return rc;
+    float *yp = nullptr;
+    if (y != nullptr) {
+        yp = find_f32(rt, y, static_cast<size_t>(t->rows) * ntok, &rc);
+        if (yp == nullptr) return rc;
+    }
+    const bool with_argmax = (flags & VQM_FUSE_ARGMAX) != 0;
+    if (yp == nullptr && (!with_argmax || (flags & VQM_FUSE_ADD))) return fail(VQM_ERR_VALUE, "y may only be NULL for an argmax without a residual");
+    if (!with_argmax && out_ids != nullptr) return fail(VQM_ERR_VALUE, "out_ids without VQM_FUSE_ARGMAX");
+    Fuse f;
+    f.flags = flags & (VQM_FUSE_ADD | VQM_FUSE_NORM | VQM_FUSE_SILU_MUL);
+    f.eps = eps;
+    if (flags & VQM_FUSE_SILU_MUL) {
+        if (x2 == nullptr) return fail(VQM_ERR_VALUE, "VQM_FUSE_SILU_MUL needs x2");
+        f.x2 = find_f32(rt, x2, static_cast<size_t>(t->cols) * ntok, &rc);
+        if (f.x2 == nullptr) return rc;
+    }
+    if (flags & VQM_FUSE_NORM) {
+        if (norm_weight == nullptr) return fail(VQM_ERR_VALUE, "VQM_FUSE_NORM needs norm_weight");
+        // the norm weights are an fp32 buffer of `cols` values, or an F32 tensor with `cols` elements (the reference keeps
+        // them as a one-dimensional F32 weight tensor)
+        auto wt = rt->tensors.find(norm_weight);
+        if (wt != rt->tensors.end()) {
+            if (wt->second.type != vqm::kF32 || static_cast<long long>(wt->second.rows) * wt->second.cols != t->cols)
+                return fail(VQM_ERR_VALUE, "%s: norm weights must be F32 with %d elements", norm_weight, t->cols);
+            f.norm_w = reinterpret_cast<const float *>(wt->second.data);
+        } else {
+            f.norm_w = find_f32(rt, norm_weight, static_cast<size_t>(t->cols), &rc);
+            if (f.norm_w == nullptr) return rc;
+        }
+        if (!(eps >= 0.0f)) return fail(VQM_ERR_VALUE, "eps must be >= 0");
+    }
+    if (out_ids != nullptr && (rc = no_capture(rt, "a blocking fused argmax")) != VQM_OK) return rc;
+    const Tensor *ts[1] = {t};
+    float *ys[1] = {yp};
+    if ((rc = launch_parts(rt, 1, ts, xp, ys, ntok, with_argmax, nullptr, &f)) != VQM_OK) return rc;
+    if (out_ids != nullptr) {
+        cudaError_t err = cudaMemcpyAsync(out_ids, rt->argmax_ids, sizeof(int) * ntok, cudaMemcpyDeviceToHost, rt->stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(rt->stream);
+        if (err != cudaSuccess) return cuda_fail("qmv_fused", err);
     }
     return VQM_OK;
 }

@@ -86,6 +86,15 @@ class Runtime:
         keep, addr, n = _ptr(data)
         _capi.check(self._lib.vqm_upload(self._h, _name(name), addr, n, int(type), int(cols), int(rows)))
 
+    def upload_file(self, name: str, path, offset: int, nbytes: int, type: int, cols: int, rows: int, threads: int = 4) -> None:
+        """The tensor's raw blocks straight from `nbytes` bytes at byte `offset` of the file `path` (for a GGUF file the
+        tensor's absolute offset): parallel reads into pinned staging overlapped with the copies to the device.  Replaces the
+        reference wrapper's mmap + upload per tensor (engine/src/vinf/cuda/qwen_runtime.py:68-86)."""
+        if offset < 0 or nbytes < 0:
+            raise ValueError("offset and nbytes must be non-negative")
+        _capi.check(self._lib.vqm_upload_file(self._h, _name(name), _name(str(path)), int(offset), int(nbytes), int(type), int(cols), int(rows),
+                                              int(threads)))
+
     def bind_tensor(self, name: str, device_ptr: int, type: int, cols: int, rows: int) -> None:
         """Registers raw blocks that already sit in device memory (not freed by the runtime)."""
         _capi.check(self._lib.vqm_bind_tensor(self._h, _name(name), ctypes.c_void_p(device_ptr), int(type), int(cols), int(rows)))
@@ -213,6 +222,17 @@ class Runtime:
         out = (ctypes.c_int * ntok)() if blocking else None
         _capi.check(self._lib.vqm_qmv_argmax(self._h, _name(weight), _name(x), _name(y), int(ntok), out))
         return list(out) if blocking else None
+
+    def qmv_fused(self, weight: str, x: str, y: str | None, ntok: int = 1, *, add: bool = False, norm: str | None = None, eps: float = 1e-6,
+                  silu_mul: str | None = None, argmax: bool = False, blocking: bool = True) -> list[int] | None:
+        """qmv with the reference's fused-QMV prologues and epilogues (engine/csrc/common/qwen_mk_abi.h:55-58): the activations
+        are silu(x) * silu_mul if `silu_mul` names a second buffer, then rms-normalised and scaled by the weights `norm`
+        (a buffer or F32 tensor of `cols` values) if given; `add` makes it y += W v; `argmax` adds the fused argmax and
+        returns the ids (blocking) or leaves them on the device."""
+        flags = (1 if add else 0) | (2 if norm is not None else 0) | (4 if argmax else 0) | (8 if silu_mul is not None else 0)
+        out = (ctypes.c_int * ntok)() if (argmax and blocking) else None
+        _capi.check(self._lib.vqm_qmv_fused(self._h, _name(weight), _name(x), _name(y), int(ntok), flags, _name(silu_mul), _name(norm), float(eps), out))
+        return list(out) if out is not None else None
 
     def argmax_result(self) -> tuple[int, int]:
         """Device addresses of the last fused argmax: (int32 ids[8], fp32 values[8])."""
