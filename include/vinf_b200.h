@@ -247,6 +247,15 @@ int vqm_qmv_push_group(vqm_runtime *rt, int n, const char *const *weights, const
 int vqm_qmv_argmax_static(int type, const void *w, int rows, int cols, const float *x, float *y, int ntok, const void *codebook,
                           int *out_ids, float *out_values, unsigned *status, void *stream);
 
+/* No counterpart in the reference.  Measures, on the current device, how many scheduler cycles a warp instruction of the
+ * kinds the matvec decoders are made of costs (one block per SM, warps_per_sm warps - a multiple of 4 in 4..32 - each
+ * running 2048 x 16 independent instructions between two clock reads).  out[0..9]: PRMT, LOP3, FFMA2 (fma.rn.f32x2),
+ * FFMA, IMAD, SHF, cvt.f32.f16, PRMT and FFMA2 alternating (per instruction), then the decode sequence of 8 packed 4-bit
+ * weights of one row with 1 and with 4 activation rows (per 8 weights).  The instruction-issue roofline of the matvec
+ * kernels is built on these numbers.  Allocates and frees a little device memory; synchronises the device. */
+#define VQM_PROBE_KINDS 10
+int vqm_probe_issue_rates(int warps_per_sm, double *out, int n);
+
 #ifdef __cplusplus
 }
 #endif

@@ -539,3 +539,17 @@ def test_a_graph_that_captured_a_prompt_pass_pins_the_activation_buffer(rt, code
         rt.synchronize()
     finally:
         rt.set_gemm_min_rows(0)
+
+
+def test_issue_rate_probe_reports_plausible_rates():
+    """The probe behind the instruction-issue roofline: every kind costs between half a cycle and a few cycles per warp
+    instruction, and the decode sequence of 8 weights costs more with 4 activation rows than with 1."""
+    from vinf_3080ti_b200.runtime import PROBE_KINDS, probe_issue_rates
+
+    rates = probe_issue_rates(16)
+    assert list(rates) == list(PROBE_KINDS)
+    for kind in PROBE_KINDS[:8]:
+        assert 0.4 <= rates[kind] <= 8.0, (kind, rates[kind])
+    assert 8.0 <= rates[PROBE_KINDS[8]] < rates[PROBE_KINDS[9]] <= 200.0
+    with pytest.raises(ValueError):
+        probe_issue_rates(5)

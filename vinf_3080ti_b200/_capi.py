@@ -78,6 +78,7 @@ SIGNATURES: dict[str, list] = {
     "vqm_qmv_group": [c_void_p, c_int, POINTER(c_char_p), c_char_p, POINTER(c_char_p), c_int],
     "vqm_qmv_push_group": [c_void_p, c_int, POINTER(c_char_p), c_char_p, POINTER(c_char_p), c_int, c_int, POINTER(c_size_t),
                            POINTER(c_int), POINTER(c_int), c_int],
+    "vqm_probe_issue_rates": [c_int, POINTER(ctypes.c_double), c_int],
     "vqm_qmv_raw": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "vqm_qmv_argmax_static": [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }

@@ -1,6 +1,11 @@
 """Builds libvinf_b200.so (the C-ABI library) for sm_100a with nvcc, in-tree.
 
-    python -m vinf_3080ti_b200.build [--force] [--jobs N]
+    python -m vinf_3080ti_b200.build [--force] [--jobs N] [--define NAME[=VALUE] ...] [--out PATH]
+
+--define passes -DNAME[=VALUE] to every translation unit: the kernels' experiment switches (VQM_ABLATE_STEP: the matvec
+pipeline without the decoders; VQM_PURE_COMPUTE: the decoders without copies and waits; VQM_NO_SCALE_PASS / VQM_NO_DOT:
+without one of the two passes of the tuned K-quant decoders) give the ablation timings quoted in profiles/.  Such a build
+goes to --out (objects beside it) and is loaded with VINF_B200_LIB=<path>; its results are wrong on purpose.
 
 Two translation units per GGUF type (the matvec kernel instantiations, plain and with the fused prologues) plus the small kernels and the
 runtime; objects go to csrc/build/, the library next to this file.  Cross-compiles without a GPU.
@@ -46,10 +51,13 @@ def up_to_date() -> bool:
     return all(src.stat().st_mtime <= built for src in _sources())
 
 
+EXTRA_DEFINES: list[str] = []
+
+
 def _compile(job: tuple[str, list[str], Path]) -> tuple[str, str]:
     name, extra, obj = job
     src = CSRC / name
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, *EXTRA_DEFINES, "-c", str(src), "-o", str(obj)]
     env = dict(os.environ)
     env.pop("CC", None)  # nvcc picks its host compiler from PATH
     env.pop("CXX", None)
@@ -59,7 +67,15 @@ def _compile(job: tuple[str, list[str], Path]) -> tuple[str, str]:
     return obj.name, done.stdout + done.stderr
 
 
-def build(force: bool = False, jobs: int | None = None, verbose: bool = False) -> Path:
+def build(force: bool = False, jobs: int | None = None, verbose: bool = False, defines: list[str] | None = None, out: Path | None = None) -> Path:
+    global OBJ, LIB
+    if defines or out:
+        if out is None:
+            raise ValueError("an experimental build (--define) needs --out, it must not replace the library")
+        LIB = Path(out).resolve()
+        OBJ = LIB.parent / (LIB.stem + "_obj")
+        EXTRA_DEFINES[:] = [f"-D{d}" for d in (defines or [])]
+        force = True
     if not force and up_to_date():
         return LIB
     OBJ.mkdir(parents=True, exist_ok=True)
@@ -71,6 +87,7 @@ def build(force: bool = False, jobs: int | None = None, verbose: bool = False) -
     work += [("vqm_matvec_type.cu", [f"-DVQM_TYPE={tid}", f"-DVQM_TYPE_NAME={tname}", "-DVQM_FUSED=1"], OBJ / f"matvec_fused_{tname}.o")
              for tid, tname in TYPES]
     work.append(("vqm_aux.cu", [], OBJ / "aux.o"))
+    work.append(("vqm_probe.cu", [], OBJ / "probe.o"))
     work.append(("vqm_gemm.cu", [], OBJ / "gemm.o"))
     work.append(("vqm_gemm_tc5.cu", [], OBJ / "gemm_tc5.o"))
     work.append(("vqm_runtime.cu", [], OBJ / "runtime.o"))
@@ -97,6 +114,8 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--jobs", type=int, default=None)
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[], metavar="NAME[=VALUE]")
+    ap.add_argument("--out", default=None)
     ns = ap.parse_args()
-    print(build(ns.force, ns.jobs, ns.verbose))
+    print(build(ns.force, ns.jobs, ns.verbose, ns.define, ns.out))
     sys.exit(0)

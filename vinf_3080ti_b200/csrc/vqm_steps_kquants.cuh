@@ -240,11 +240,19 @@ struct QuarterStep {
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 d2[r] = lds64(el + r * 4 * kEntry + Q * 8);
+#ifdef VQM_X_NO_QUARTER
+                q[r] = first[r].qh + Q;
+#else
                 q[r] = F::template quarter<Q>(first[r]);
+#endif
             }
             quad_dot(q, d2, x_first + Q * 32 * 4, acc);
 #pragma unroll
+#ifdef VQM_X_NO_QUARTER
+            for (int r = 0; r < NR; ++r) q[r] = second[r].qh + Q;
+#else
             for (int r = 0; r < NR; ++r) q[r] = F::template quarter<Q>(second[r]);
+#endif
             quad_dot(q, d2, x_second + Q * 32 * 4, acc);
         }
 
@@ -279,7 +287,12 @@ struct QuarterStep {
 #pragma unroll
                 for (int r = 0; r < NR; ++r) {
                     const uint32_t a = stage + r * SLOT + ((d0 + r * rb16) & 15u) + lane_off, b = a & ~3u;
+#ifdef VQM_X_NO_LOAD
+                    first[r] = typename F::Words{a, b, d0};
+                    second[r] = typename F::Words{b, a, rb16};
+#else
                     F::load(b + 4 * h, b + 4 - 4 * h, (a & 2u) << 3, d2nd, h, first[r], second[r]);
+#endif
                 }
                 const uint32_t el = scratch + blk * kEntry + (h * 2 + (jj >> 1)) * 32;
                 const uint32_t x_first = xs + (blk * 256 + 128 * h + 8 * jj + 4 * h) * 4;

@@ -49,6 +49,19 @@ def reference_codebooks() -> dict[str, bytes]:
     return books
 
 
+PROBE_KINDS = ("PRMT", "LOP3", "FFMA2", "FFMA", "IMAD", "SHF", "cvt.f32.f16", "PRMT+FFMA2 alternating",
+               "decode of 8 Q4_K weights, 1 activation row", "decode of 8 Q4_K weights, 4 activation rows")
+
+
+def probe_issue_rates(warps_per_sm: int = 16) -> dict[str, float]:
+    """Scheduler cycles per warp instruction (last two entries: per 8 weights of a row) on the current device, measured by
+    the library's probe kernel.  What the instruction-issue roofline of the matvec kernels is built on."""
+    lib = _capi.load()
+    out = (ctypes.c_double * len(PROBE_KINDS))()
+    _capi.check(lib.vqm_probe_issue_rates(int(warps_per_sm), out, len(PROBE_KINDS)))
+    return dict(zip(PROBE_KINDS, (float(v) for v in out)))
+
+
 class Runtime:
     """Named raw-GGUF weight tensors and fp32 buffers in B200 HBM, with y = W x and argmax on them."""
 
