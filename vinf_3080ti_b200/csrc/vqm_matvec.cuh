@@ -40,6 +40,7 @@
 #include "vqm_steps.cuh"
 #include "vqm_steps_kquants.cuh"
 #include "vqm_steps_iq4.cuh"
+#include "vqm_steps_grid.cuh"
 
 namespace vqm {
 
@@ -53,7 +54,10 @@ constexpr int kBarrierBytes = 1024;            // mbarriers and counters at the 
 #endif
 constexpr bool kFusedBuild = VQM_FUSED != 0;
 
-__host__ __device__ constexpr int table_bytes_padded(int type) { return (grid_bytes(type) + 15) / 16 * 16; }
+// lookup tables at the front of shared memory: the type's codebook or level table, then (codebook types) the sign table
+__host__ __device__ constexpr int table_bytes_padded(int type) {
+    return (grid_bytes(type) + 15) / 16 * 16 + (grid_is_codebook(type) ? kSignTableBytes : 0);
+}
 
 // Blocks per SM the register allocation aims for: two, except for the tall chunks of wide passes (their sums alone
 // take RW * M register pairs).  One-row chunks always get two, which the column split of short launches counts on.
@@ -372,6 +376,8 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
         if constexpr (grid_is_codebook(TYPE)) {
             const uint32_t *src = reinterpret_cast<const uint32_t *>(a.codebook);
             for (int i = threadIdx.x; i < grid_bytes(TYPE) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(table)[i] = src[i];
+            uint2 *sign_table = reinterpret_cast<uint2 *>(table + (grid_bytes(TYPE) + 15) / 16 * 16);
+            for (int i = threadIdx.x; i < 256; i += blockDim.x) sign_table[i] = sign_table_entry(static_cast<uint32_t>(i), signs_have_parity(TYPE));
         } else {
             if (threadIdx.x < 16) reinterpret_cast<float *>(table)[threadIdx.x] = kIq4Levels[threadIdx.x];
         }
