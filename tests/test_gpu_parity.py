@@ -477,12 +477,16 @@ def test_group_launch_error_contract(rt):
         rt.qmv_group(["gb"], "x", ["ya"], 9)
 
 
+@pytest.mark.parametrize("rows,ntok", [(200, 130), (300, 300), (200, 700)], ids=lambda v: str(v))
 @pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
-def test_prompt_gemm_tcgen05_matches_the_matvec_path_for_every_type(rt, codebooks, t):
-    """Passes of 128+ activation rows take the tcgen05 kernel (accumulators in tensor memory): 200 x 1024 weights (a
-    partial tile of rows), 130 activation rows (a partial tile of 512), same tolerance as the warp-level kernel."""
-    rng = np.random.default_rng(5100 + int(t))
-    rows, cols, ntok = 200, 1024, 130
+def test_prompt_gemm_tcgen05_matches_the_matvec_path_for_every_type(rt, codebooks, t, rows, ntok):
+    """Passes of 64+ activation rows take the tcgen05 kernel (accumulators in tensor memory), in each of its block shapes:
+    up to 256 activation rows (one accumulator per block); more than that (two accumulators: 256 weight rows per block,
+    or 512 activation rows for the types whose raw blocks for 256 rows do not fit in shared memory); several tiles of
+    activation rows.  The weight rows end inside a tile, and inside its first half.  Same tolerance as the warp-level
+    kernel."""
+    rng = np.random.default_rng(5100 + int(t) + ntok)
+    cols = 1024
     raw = synthetic_blocks(t, rows, cols, rng)
     x = synthetic_activations(ntok, cols, rng)
     ref = run_qmv(rt, raw, t, rows, cols, x)  # fp32 matvec, groups of 8
@@ -497,6 +501,37 @@ def test_prompt_gemm_tcgen05_matches_the_matvec_path_for_every_type(rt, codebook
     assert np.all(np.abs(got - ref) <= 3e-3 * np.abs(ref).max())
     oracle = O.matvec(raw, int(t), rows, cols, x, codebooks)
     assert rel_l2(got, oracle) <= 2e-3  # fp16 rounding of both operands
+
+
+@pytest.mark.parametrize("ntok", [256, 512])
+@pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
+def test_prompt_gemm_tiles_hold_the_dequantised_weights_rounded_to_fp16(rt, codebooks, t, ntok):
+    """One-hot activation rows read the fp16 weight tiles of the tcgen05 kernel back: activation row k = unit vector k
+    makes output [k][row] the weight [row][k] as the kernel's producers stored it.  It must be the exact dequantised value
+    rounded to fp16 (to nearest even), for the generic decoders and for the fast per-block ones alike, in the block
+    shapes for up to 256 and for more activation rows."""
+    rng = np.random.default_rng(6200 + int(t))
+    rows, cols = 300, 512
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = np.zeros((ntok, cols), dtype=np.float32)
+    x[np.arange(ntok), np.arange(ntok)] = 1.0
+    rt.upload("w", raw, int(t), cols, rows)
+    rt.alloc("x", ntok * cols)
+    rt.alloc("y", ntok * rows)
+    rt.write("x", x)
+    rt.set_gemm_min_rows(64)
+    try:
+        rt.qmv("w", "x", "y", ntok)
+        rt.synchronize()
+        got = rt.read_array("y").reshape(ntok, rows)
+    finally:
+        rt.set_gemm_min_rows(0)
+    w = O.dequantize(raw, int(t), rows * cols, codebooks).reshape(rows, cols)
+    with np.errstate(over="ignore"):
+        want = w[:, :ntok].astype(np.float16).astype(np.float32).T
+    finite = np.isfinite(want)  # synthetic F32 / F16 values beyond the fp16 range would be inf in the tile
+    assert finite.mean() > 0.99
+    assert np.array_equal(got[finite], want[finite])
 
 
 @pytest.mark.parametrize("t,rows,cols,ntok", [

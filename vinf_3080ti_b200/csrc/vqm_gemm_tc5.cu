@@ -2,35 +2,71 @@
 //
 // Same contract as the warp-level kernel in vqm_gemm.cu (replaces the reference's vinf_qgemm_kernel,
 // engine/csrc/megakernel/qwen_runtime.cu:655-769: fp16 operands, fp32 accumulation), built on tcgen05:
-//   * a block owns 128 weight rows (the MMA's M) and 512 activation rows (two accumulators of N = 256); the fp32
-//     accumulators live in tensor memory (128 lanes x 512 columns, the whole TMEM of an SM, so one block per SM);
+//   * a block owns 128 or 256 weight rows (one or two MMA M-halves) and 256 or 512 activation rows, as one or two
+//     accumulators of 128 x 256 fp32 in tensor memory (at most 512 columns, the whole TMEM of an SM: one block per SM);
+//     the shapes and when each is used are listed at stage_bytes below;
+//   * the raw weight bytes come in by bulk copies (1-D TMA, no multicast), 256 columns of the block's rows at a time
+//     into a ring of two shared-memory buffers, one copy per row issued by the row's first decoder thread, so that the
+//     decoders never wait for global memory (types whose 256 columns are too wide for the ring - Q8_0, F16, F32 - are
+//     decoded straight from global memory);
 //   * K is walked in stages of 64, each filled and consumed as two halves of 32 (four pipeline slots in two stage
-//     buffers): warps 0-15 dequantise the 128 x 32 weight half-tile with the exact block decoders (four threads per
-//     row, one chunk of 8 weights each) and store it as fp16 in the K-major 128-byte-swizzled layout the tensor core
-//     reads; warps 16-18 copy the 512 x 32 fp16 activation half-tile into the same layout with cp.async (the copies of
-//     three slots in flight per thread); both sides make their writes visible to the async proxy and arrive on the
-//     slot's "full" mbarrier;
-//   * one thread of warp 19 issues, per slot, 2 K-steps x 2 accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
+//     buffers): warps 0-15 dequantise the weight half-tile (four threads per row, one chunk of 8 weights each and row
+//     half) with the exact block decoders - for Q4_K / Q5_K with a per-block header and constant shifts, see FastHeader -
+//     and store it as fp16 in the K-major 128-byte-swizzled layout the tensor core reads; warps 16-18 copy the fp16
+//     activation half-tile into the same layout with cp.async (the copies of three slots in flight per thread); both
+//     sides make their writes visible to the async proxy and arrive, once per warp, on the slot's "full" mbarrier;
+//   * one thread of warp 19 issues, per slot, 2 K-steps x the accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
 //     K = 16) from shared-memory descriptors and commits them to the slot's "empty" mbarrier, which hands the slot
 //     back to the producers, so tile production runs up to three slots ahead of the MMAs;
 //   * after the last commit, warps 0-3 read the accumulators with tcgen05.ld (warp w owns lanes 32w..32w+31, one
-//     weight row per thread) and store y; a warp stores 32 consecutive rows of one activation row, 128 bytes.
+//     weight row per thread and row half) and store y; a warp stores 32 consecutive rows of one activation row, 128 bytes.
+// Where the time goes (Q4_K 17408 x 5120, 512 activation rows, 141 us with the activation conversion; experiment builds
+// with VQM_TC5_ABLATE): the MMA issue loop alone, never waiting, 81 us (640 MMAs of 128 x 256 x 16 at about 1.7 GHz are
+// 50 us; the rest is the conversion kernel, the prologue and the epilogue that nothing overlaps); with the barriers but
+// neither decode nor activation copies 103 us; without the activation copies 126 us; without the decode 135 us.
 // Every mbarrier wait is bounded: on expiry the block records a status code, everybody falls through to the end, and
 // the tensor memory is released before the block returns.
 #include <cuda_fp16.h>
 
 #include "vqm_formats.cuh"
 #include "vqm_kernels.h"
+#include "vqm_steps.cuh"
+
+#ifndef VQM_TC5_ABLATE
+#define VQM_TC5_ABLATE 0  // experiment builds (wrong results): 1 = fast decoders store zeros, 2 = no activation copies,
+                         // 4 = no proxy fence by the producers, 8 = only the MMA issue loop runs, without waiting
+#endif
 
 namespace vqm {
 namespace {
 
-constexpr int kTM = 128, kTN = 512, kTK = 64, kTStages = 2;
-constexpr int kTA = kTM * kTK * 2, kTB = kTN * kTK * 2, kTStage = kTA + kTB;  // 16 KB + 64 KB
+// A block computes kTM * MR weight rows by kTNH * NH activation rows: MR x NH accumulators of 128 x 256 in tensor memory
+// (MR * NH <= 2: 512 columns).  The three shapes in use:
+//   MR 1, NH 1  up to 256 activation rows;
+//   MR 2, NH 1  more than that, for the types with a fast decoder whose raw-block ring for 256 rows fits beside the tiles
+//               (Q4_K): 256 weight rows per block halve what the blocks together pull out of L2 for the activations
+//               (every block reads its activation tile once per weight tile: 713 MB for 17408 x 5120 x 512);
+//   MR 1, NH 2  more than that, for the other types.
+constexpr int kTM = 128, kTNH = 256, kTK = 64, kTStages = 2;
+constexpr int kTA1 = kTM * kTK * 2, kTB1 = kTNH * kTK * 2;  // 16 KB per 128 weight rows, 32 KB per 256 activation rows
+__host__ __device__ constexpr int stage_bytes(int mr, int nh) { return mr * kTA1 + nh * kTB1; }
 constexpr int kTSlots = 2 * kTStages;  // half stages
 constexpr int kTThreads = 640;
 constexpr int kAThreads = 512, kBThreads = 96;
-constexpr uint32_t kTmemCols = 512;
+// Raw-block ring: a "column" is 256 weight columns of the 128 rows; a row's bytes of one column are contiguous.
+constexpr int kRawCols = 256;
+__host__ __device__ constexpr int raw_run_bytes(int type) { return kRawCols / chunk_block(type) * chunk_block_bytes(type); }
+// slot of one row: the run, up to 14 bytes in front (the copy starts at the 16-byte boundary below), the decoders' reads
+// of up to 8 bytes behind, rounded to 16
+__host__ __device__ constexpr int raw_slot_bytes(int type) { return (raw_run_bytes(type) + 14 + 8 + 15) / 16 * 16; }
+__host__ __device__ constexpr bool raw_staged(int type) { return raw_run_bytes(type) <= 210; }  // every type up to Q6_K; not Q8_0, F16, F32 (the ring would not fit)
+__host__ __device__ constexpr int raw_ring_bytes(int type, int mr) { return raw_staged(type) ? 2 * mr * kTM * raw_slot_bytes(type) : 0; }
+__host__ __device__ constexpr int table_bytes16(int type) { return grid_bytes(type) > 0 ? (grid_bytes(type) + 15) / 16 * 16 : 16; }
+__host__ __device__ constexpr size_t tc5_smem_bytes(int type, int mr, int nh) {
+    return table_bytes16(type) + 1024 + static_cast<size_t>(kTStages) * stage_bytes(mr, nh) + raw_ring_bytes(type, mr);
+}
+// 256 weight rows per block need the raw ring for 256 rows (reading them from global memory per chunk is too slow there)
+__host__ __device__ constexpr bool fits_two_row_halves(int type) { return raw_staged(type) && tc5_smem_bytes(type, 2, 1) <= 227 * 1024; }
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -51,16 +87,42 @@ __device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: the warp may sleep in hardware for up to `ns` before the instruction returns false,
+// instead of taking issue slots from the warps that have work.
+__device__ __forceinline__ bool bar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait; also gives up as soon as another thread of the block has (`failed` is a shared flag).
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int *failed) {
 #pragma unroll 1
-    for (int i = 0; i < (1 << 22); ++i) {
-        if (bar_try(bar, parity)) return true;
+    for (int i = 0; i < (1 << 21); ++i) {  // about a second at the least, several at the most
+        if (bar_try_hint(bar, parity, 2000u)) return true;
         if (*failed) return false;
-        if (i > 64) __nanosleep(32);
+        if (i > 4096) __nanosleep(200);  // only a wait that is already far beyond a pipeline step backs off
     }
     *failed = 1;
     return false;
+}
+
+// Warp-wide forms (every lane of the warp calls them together).
+//   warp_wait: every lane polls and the warp votes, so that it takes one branch even when a wait gives up.  (Polling by
+//              lane 0 alone with a broadcast was measured: slower, 204 instead of 141 us for Q4_K 17408 x 5120 x 512.)
+//   warp_arrive: one arrive per warp instead of 32 atomics on the barrier word, after the warp's own writes (and proxy
+//              fences); __syncwarp orders them before lane 0's arrive.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *failed) {
+    return __all_sync(0xFFFFFFFFu, bar_wait(bar, parity, failed) ? 1 : 0) != 0;
+}
+__device__ __forceinline__ void warp_arrive(uint32_t bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) bar_arrive(bar);
 }
 
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 64 fp16 = 128 bytes, groups of 8
@@ -84,29 +146,115 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- fast chunk decoders of the producer warps --------------------------------------------------------------------------
+// The generic block decoder (deq8) unpacks the block header for every chunk of 8 weights.  A producer thread stays on one
+// row and walks a block's eight 32-column slots in order, so for the types below the header is unpacked once per block
+// and a chunk is a load of 8 bytes, one byte permute per weight and packed fp32 arithmetic - the same operations in the
+// same order as deq8, so the fp16 tiles are bit-identical to what the generic path stores.
+template <int N>
+struct Int {
+    static constexpr int value = N;
+};
+__host__ __device__ constexpr bool has_fast_chunk(int type) { return type == kQ4_K || type == kQ5_K; }
+
+__device__ __forceinline__ uint32_t f16x2_of(f32x2 v) {  // (lo, hi) -> two fp16 in one word, round to nearest even
+    float lo, hi;
+    unpack2(v, lo, hi);
+    uint32_t h;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(hi), "f"(lo));
+    return h;
+}
+// the four bytes of `w` times dl plus nml (packed), as fp16
+__device__ __forceinline__ void bytes_fma_f16(uint32_t w, f32x2 neg_magic, f32x2 dl, f32x2 nml, uint32_t &h0, uint32_t &h1) {
+    h0 = f16x2_of(fma2(bytes_to_pair<0, 1>(w, neg_magic), dl, nml));
+    h1 = f16x2_of(fma2(bytes_to_pair<2, 3>(w, neg_magic), dl, nml));
+}
+
 template <int TYPE>
+struct FastHeader;
+
+// Q4_K / Q5_K (engine/csrc/common/qwen_quant.cuh:78-86, 171-196): d, dmin, 12 bytes of 6-bit scales and minimums; slot G of
+// the block is its sub-block G (32 weights with one scale and one minimum), weight = d * sc * q - dmin * mn.
+template <int TYPE>
+struct FastHeaderK45 {
+    uint32_t sc_lo, sc_hi, mn_lo, mn_hi;  // scales / minimums of sub-blocks 0..3 and 4..7, one per byte
+    float d, ndmin;
+    uint32_t qh0, qh1;  // Q5_K: the thread's 8 bytes of fifth bits (bit G belongs to slot G)
+    __device__ __forceinline__ void load(uint32_t blk, int quarter) {
+        const uint4 h = lds128u(blk);  // blocks of these types are 16-byte aligned
+        d = half_bits_to_float(h.x & 0xFFFFu);
+        ndmin = -half_bits_to_float(h.x >> 16);
+        sc_lo = h.y & 0x3F3F3F3Fu;
+        mn_lo = h.z & 0x3F3F3F3Fu;
+        sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+        mn_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+        if constexpr (TYPE == kQ5_K) {
+            const unsigned long long q = lds64(blk + 16 + 8 * quarter);
+            qh0 = static_cast<uint32_t>(q), qh1 = static_cast<uint32_t>(q >> 32);
+        }
+    }
+    template <int G>
+    __device__ __forceinline__ void chunk(uint32_t blk, int quarter, uint32_t (&h)[4]) const {
+        const float dl = d * byte_to_float<G & 3>(G < 4 ? sc_lo : sc_hi);
+        const float nml = ndmin * byte_to_float<G & 3>(G < 4 ? mn_lo : mn_hi);  // -(dmin * mn), exactly
+        const unsigned long long q = lds64(blk + (TYPE == kQ4_K ? 16 : 48) + 32 * (G >> 1) + 8 * quarter);
+        uint32_t w0 = static_cast<uint32_t>(q), w1 = static_cast<uint32_t>(q >> 32);
+        if constexpr (G & 1) w0 >>= 4, w1 >>= 4;
+        w0 &= 0x0F0F0F0Fu, w1 &= 0x0F0F0F0Fu;
+        if constexpr (TYPE == kQ5_K) {
+            w0 |= (G <= 4 ? qh0 << (4 - G) : qh0 >> (G - 4)) & 0x10101010u;
+            w1 |= (G <= 4 ? qh1 << (4 - G) : qh1 >> (G - 4)) & 0x10101010u;
+        }
+        const f32x2 neg_magic = pack2(-8388608.0f, -8388608.0f), dl2 = pack2(dl, dl), nml2 = pack2(nml, nml);
+        bytes_fma_f16(w0, neg_magic, dl2, nml2, h[0], h[1]);
+        bytes_fma_f16(w1, neg_magic, dl2, nml2, h[2], h[3]);
+    }
+};
+template <>
+struct FastHeader<kQ4_K> : FastHeaderK45<kQ4_K> {};
+template <>
+struct FastHeader<kQ5_K> : FastHeaderK45<kQ5_K> {};
+// (types without a fast decoder never instantiate this)
+template <int TYPE>
+struct FastHeader {
+    __device__ __forceinline__ void load(uint32_t, int) {}
+    template <int G>
+    __device__ __forceinline__ void chunk(uint32_t, int, uint32_t (&)[4]) const {}
+};
+
+template <int TYPE, int MR, int NH>
 __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *w, const __half *xh, float *y, int rows, int cols,
                                                                  long long row_bytes, int ntok, const uint8_t *codebook,
                                                                  unsigned *status) {
     constexpr int CPB = chunk_block(TYPE) / 8, BB = chunk_block_bytes(TYPE);
-    constexpr int TABLE = grid_bytes(TYPE) > 0 ? (grid_bytes(TYPE) + 15) / 16 * 16 : 16;
+    constexpr int TABLE = table_bytes16(TYPE);
+    constexpr int kTStage = stage_bytes(MR, NH), kTA = MR * kTA1, kTN = NH * kTNH;
+    constexpr uint32_t kTmemCols = 256 * MR * NH;
+    static_assert(MR * NH <= 2, "512 columns of tensor memory");
     extern __shared__ uint8_t tc5_raw[];
-    __shared__ __align__(8) uint64_t s_full[kTSlots], s_empty[kTSlots], s_done;
+    __shared__ __align__(8) uint64_t s_full[kTSlots], s_empty[kTSlots], s_done, s_raw_full[2], s_raw_empty[2];
     __shared__ uint32_t s_tmem;
     __shared__ int s_failed;
     // table first, then the stages on a 1024-byte boundary (the swizzle works on absolute shared-memory address bits)
     uint8_t *table = tc5_raw;
     const uint32_t tiles = (s32(tc5_raw) + TABLE + 1023u) & ~1023u;
+    constexpr bool kStaged = raw_staged(TYPE);
+    constexpr int RSLOT = raw_slot_bytes(TYPE), RUN = raw_run_bytes(TYPE);
+    const uint32_t raw_ring = tiles + kTStages * kTStage;  // two buffers of MR * kTM row slots
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * kTM, tok0 = blockIdx.y * kTN;
+    const int row0 = blockIdx.x * (kTM * MR), tok0 = blockIdx.y * kTN;
     const int n_k = cols / kTK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTSlots; ++s) {
-            bar_init(s32(&s_full[s]), kAThreads + kBThreads);
+            bar_init(s32(&s_full[s]), (kAThreads + kBThreads) / 32);  // one arrive per producer / loader warp
             bar_init(s32(&s_empty[s]), 1);
         }
         bar_init(s32(&s_done), 1);
+        for (int b = 0; b < 2; ++b) {
+            bar_init(s32(&s_raw_full[b]), kTM);         // one arrive (with its byte count) per first thread of a row
+            bar_init(s32(&s_raw_empty[b]), kAThreads / 32);  // every decoder warp is done with the buffer
+        }
         s_failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -118,7 +266,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
             if (threadIdx.x < 16) reinterpret_cast<float *>(table)[threadIdx.x] = kIq4Levels[threadIdx.x];
         }
     }
-    if (warp == 0) {  // tensor memory: all 512 columns (one block per SM)
+    if (warp == 0) {  // tensor memory: 256 columns per accumulator (one block per SM)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&s_tmem)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -129,42 +277,160 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     volatile int *failed = &s_failed;
 
     const int n_slots = 2 * n_k;  // slot q of the pipeline: stage (q / 2) % 2, K half q % 2
+#if VQM_TC5_ABLATE & 8
+    if (warp < 19) {
+    } else
+#endif
     if (warp < 16) {
         // ---- weight half-tile: four threads per row, one chunk each; chunk c of the stage (8 weights, 16 bytes of fp16)
         //      goes to 16-byte slot c ^ (row % 8) of the row
         //      (the four threads of a row are neighbours in a warp: their global loads fall into the same sectors)
-        const int r = threadIdx.x >> 2, quarter = threadIdx.x & 3;
-        const bool valid = row0 + r < rows;
-        const uint8_t *w_row = w + static_cast<size_t>(valid ? row0 + r : 0) * row_bytes;
-        for (int q = 0; q < n_slots; ++q) {
-            const int slot = q % kTSlots;
-            if (!bar_wait(s32(&s_empty[slot]), ((q / kTSlots) & 1) ^ 1, failed)) break;
-            const uint32_t a_row = tiles + (slot >> 1) * kTStage + r * 128;
-            {
-                const int c = (slot & 1) * 4 + quarter;   // chunk within the stage
-                const int kc = (q >> 1) * (kTK / 8) + c;   // chunk within the row
-                float v[8];
-                if (valid) {
-                    const uint8_t *blk = w_row + static_cast<size_t>(kc / CPB) * BB;
-                    deq8<TYPE>(blk, kc % CPB, v, table);
-                    // the row's bytes of the next stages: into L2 -> L1 ahead of use (hint only)
-                    constexpr int kAhead = CPB == 32 ? BB : 4 * BB;
-                    if (quarter == 0 && static_cast<long long>(kc / CPB) * BB + kAhead < row_bytes)
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(blk + kAhead));
-                } else {
+        const int r = threadIdx.x >> 2, quarter = threadIdx.x & 3;  // rows r + 128 * mr of the block
+        bool valid[MR];
+        const uint8_t *w_row[MR];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
-                }
-                __half2 h[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-                const uint4 pk = *reinterpret_cast<const uint4 *>(h);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_row + ((c ^ (r & 7)) << 4)), "r"(pk.x), "r"(pk.y), "r"(pk.z),
-                             "r"(pk.w)
-                             : "memory");
-            }
+        for (int mr = 0; mr < MR; ++mr) {
+            valid[mr] = row0 + mr * kTM + r < rows;
+            w_row[mr] = w + static_cast<size_t>(valid[mr] ? row0 + mr * kTM + r : 0) * row_bytes;
+        }
+        // One slot of this thread: wait until the MMAs that read the slot's previous contents are done, store the 8 fp16
+        // weights of chunk `quarter` of the half stage for each of its rows (swizzled), make them visible to the tensor
+        // core, arrive.
+        auto slot_wait = [&](int q) -> bool { return warp_wait(s32(&s_empty[q % kTSlots]), ((q / kTSlots) & 1) ^ 1, failed); };
+        auto slot_put = [&](int q, int mr, const uint32_t (&h)[4]) {
+            const int slot = q % kTSlots, c = (slot & 1) * 4 + quarter;  // chunk within the stage
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tiles + (slot >> 1) * kTStage + (mr * kTM + r) * 128 + ((c ^ (r & 7)) << 4)),
+                         "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3])
+                         : "memory");
+        };
+        auto slot_done = [&](int q) {
+#if !(VQM_TC5_ABLATE & 4)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            bar_arrive(s32(&s_full[slot]));
+#endif
+            warp_arrive(s32(&s_full[q % kTSlots]));
+        };
+        auto to_f16 = [](const float (&v)[8], uint32_t (&h)[4]) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __half2 p = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+                h[e] = *reinterpret_cast<const uint32_t *>(&p);
+            }
+        };
+        if constexpr (!kStaged) {
+            static_assert(kStaged || MR == 1, "two row halves only with the raw ring");
+            for (int q = 0; q < n_slots; ++q) {
+                if (!slot_wait(q)) break;
+                const int kc = (q >> 1) * (kTK / 8) + (q & 1) * 4 + quarter;  // chunk within the row
+                uint32_t h[4] = {0u, 0u, 0u, 0u};
+                if (valid[0]) {
+                    float v[8];
+                    deq8<TYPE>(w_row[0] + static_cast<size_t>(kc / CPB) * BB, kc % CPB, v, table);
+                    to_f16(v, h);
+                }
+                slot_put(q, 0, h);
+                slot_done(q);
+            }
+        } else {
+            // Raw ring: column `col` (256 weight columns) of this thread's rows goes to buffer col % 2.  The first thread of a
+            // row issues the copies of its rows; the bytes keep their position inside their 16-byte line.
+            constexpr int kSlotsPerCol = 2 * kRawCols / kTK;  // 8
+            const int n_raw = (cols + kRawCols - 1) / kRawCols;
+            int raw_issued = 0;  // columns this thread has queued copies for (first thread of a row only)
+            int raw_taken = 0;   // columns whose bytes this thread has waited for
+            auto issue_raw = [&](int col) -> bool {  // the whole warp calls it; true unless a wait gave up
+                const int b = col & 1;
+                if (col >= 2 && !warp_wait(s32(&s_raw_empty[b]), ((col >> 1) - 1) & 1, failed)) return false;
+                if (quarter == 0) {
+                    raw_issued = col + 1;
+                    const long long at = static_cast<long long>(col) * RUN;
+                    const uint32_t run = row_bytes - at < RUN ? static_cast<uint32_t>(row_bytes - at) : static_cast<uint32_t>(RUN);
+                    const uint32_t bar = s32(&s_raw_full[b]);
+                    uintptr_t p[MR];
+                    uint32_t bytes[MR], total = 0;
+#pragma unroll
+                    for (int mr = 0; mr < MR; ++mr) {
+                        p[mr] = reinterpret_cast<uintptr_t>(w_row[mr]) + static_cast<uintptr_t>(at);
+                        bytes[mr] = valid[mr] ? ((static_cast<uint32_t>(p[mr]) & 15u) + run + 15u) & ~15u : 0u;
+                        total += bytes[mr];
+                    }
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(total) : "memory");
+#pragma unroll
+                    for (int mr = 0; mr < MR; ++mr)
+                        if (bytes[mr])
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                             raw_ring + ((b * MR + mr) * kTM + r) * RSLOT),
+                                         "l"(p[mr] & ~static_cast<uintptr_t>(15)), "r"(bytes[mr]), "r"(bar)
+                                         : "memory");
+                }
+                return true;
+            };
+            // Before slot g of column col.  Column col + 1 goes into the buffer column col - 1 left two slots earlier: by then
+            // every decoder thread has normally handed it back, so the wait inside does not hold the row's first thread up.
+            auto slot_begin = [&](int col, int g) -> bool {
+                if (g == 2 && col >= 1 && col + 1 < n_raw && !issue_raw(col + 1)) return false;
+                return slot_wait(col * kSlotsPerCol + g);
+            };
+            bool alive = issue_raw(0) && (n_raw < 2 || issue_raw(1));
+            for (int col = 0; alive && col < n_raw; ++col) {
+                if (!warp_wait(s32(&s_raw_full[col & 1]), (col >> 1) & 1, failed)) break;  // every lane: it reads the bytes
+                raw_taken = col + 1;
+                uint32_t blk[MR];  // the rows' blocks of this column
+#pragma unroll
+                for (int mr = 0; mr < MR; ++mr)
+                    blk[mr] = raw_ring + (((col & 1) * MR + mr) * kTM + r) * RSLOT +
+                              (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(w_row[mr]) + static_cast<uintptr_t>(col) * RUN) & 15u);
+                if constexpr (has_fast_chunk(TYPE)) {
+                    // one block per column; the block header is unpacked once, the eight slots are unrolled so that every
+                    // shift and byte position is a constant
+                    FastHeader<TYPE> hdr[MR];
+#pragma unroll
+                    for (int mr = 0; mr < MR; ++mr) hdr[mr].load(blk[mr], quarter);
+                    auto one = [&](auto g_tag) -> bool {
+                        constexpr int G = decltype(g_tag)::value;
+                        if (!slot_begin(col, G)) return false;
+#pragma unroll
+                        for (int mr = 0; mr < MR; ++mr) {
+                            uint32_t h[4] = {0u, 0u, 0u, 0u};
+#if !(VQM_TC5_ABLATE & 1)
+                            if (valid[mr]) hdr[mr].template chunk<G>(blk[mr], quarter, h);
+#endif
+                            slot_put(col * kSlotsPerCol + G, mr, h);
+                        }
+                        slot_done(col * kSlotsPerCol + G);
+                        return true;
+                    };
+                    alive = one(Int<0>{}) && one(Int<1>{}) && one(Int<2>{}) && one(Int<3>{}) && one(Int<4>{}) && one(Int<5>{}) && one(Int<6>{}) &&
+                            one(Int<7>{});
+                } else {
+                    const int slots_here = n_slots - col * kSlotsPerCol < kSlotsPerCol ? n_slots - col * kSlotsPerCol : kSlotsPerCol;
+#pragma unroll 1
+                    for (int g = 0; g < slots_here; ++g) {
+                        if (!slot_begin(col, g)) {
+                            alive = false;
+                            break;
+                        }
+                        const int in_col = g * 4 + quarter;  // chunk within the column
+#pragma unroll
+                        for (int mr = 0; mr < MR; ++mr) {
+                            uint32_t h[4] = {0u, 0u, 0u, 0u};
+                            if (valid[mr]) {
+                                float v[8];
+                                deq8<TYPE>(static_cast<const uint8_t *>(__cvta_shared_to_generic(blk[mr] + (in_col / CPB) * BB)), in_col % CPB, v, table);
+                                to_f16(v, h);
+                            }
+                            slot_put(col * kSlotsPerCol + g, mr, h);
+                        }
+                        slot_done(col * kSlotsPerCol + g);
+                    }
+                }
+                if (alive) warp_arrive(s32(&s_raw_empty[col & 1]));  // hand the buffer back
+            }
+            // Only after a wait gave up: copies this thread queued and nobody waited for must land before the block may
+            // leave (bounded; the columns complete in order).
+            for (int col = raw_taken; col < raw_issued; ++col) {
+#pragma unroll 1
+                for (int i = 0; i < (1 << 16) && !bar_try(s32(&s_raw_full[col & 1]), (col >> 1) & 1); ++i) __nanosleep(64);
+            }
         }
     } else if (warp < 19) {
         // ---- activation half-tile: 512 rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist and are zero.
@@ -174,13 +440,17 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
         bool alive = true;
         auto issue = [&]() {  // copies of slot `issued`, once the MMAs that read its previous contents are done
             const int slot = issued % kTSlots;
-            if (!bar_wait(s32(&s_empty[slot]), ((issued / kTSlots) & 1) ^ 1, failed)) {
+            if (!warp_wait(s32(&s_empty[slot]), ((issued / kTSlots) & 1) ^ 1, failed)) {
                 alive = false;
                 return;
             }
             const uint32_t b_tile = tiles + (slot >> 1) * kTStage + kTA;
             const __half *src = xh + static_cast<size_t>(tok0) * cols + (issued >> 1) * kTK + (slot & 1) * 32;
+#if VQM_TC5_ABLATE & 2
+            for (int i = b; i < 0; i += kBThreads) {
+#else
             for (int i = b; i < kTN * 4; i += kBThreads) {
+#endif
                 const int n = i >> 2, c = (slot & 1) * 4 + (i & 3);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_tile + n * 128 + ((c ^ (n & 7)) << 4)),
                              "l"(src + static_cast<size_t>(n) * cols + (i & 3) * 8)
@@ -197,23 +467,28 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
             else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
             else asm volatile("cp.async.wait_group 0;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            bar_arrive(s32(&s_full[q % kTSlots]));
+            warp_arrive(s32(&s_full[q % kTSlots]));
             if (issued < n_slots) issue();
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (lane == 0) {
-        // ---- MMA issue: accumulator 0 (activation rows 0..255) at column 0, accumulator 1 at column 256
+        // ---- MMA issue: accumulator (mr, nh) at column (mr * NH + nh) * 256
         for (int q = 0; q < n_slots; ++q) {
             const int slot = q % kTSlots;
+#if !(VQM_TC5_ABLATE & 8)
             if (!bar_wait(s32(&s_full[slot]), (q / kTSlots) & 1, failed)) break;
+#endif
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t a_desc = sw128_desc(tiles + (slot >> 1) * kTStage), b_desc = sw128_desc(tiles + (slot >> 1) * kTStage + kTA);
 #pragma unroll
             for (int jj = 0; jj < 2; ++jj) {  // 32 bytes further along K inside the swizzled rows per step
                 const int j = (slot & 1) * 2 + jj;
                 const uint32_t acc = (q | jj) != 0;
-                mma_f16(tmem, a_desc + 2 * j, b_desc + 2 * j, acc);
-                mma_f16(tmem + 256, a_desc + 2 * j, b_desc + 2 * j + ((256 * 128) >> 4), acc);
+#pragma unroll
+                for (int mr = 0; mr < MR; ++mr)
+#pragma unroll
+                    for (int nh = 0; nh < NH; ++nh)  // accumulator (mr, nh): 128 weight rows x 256 activation rows
+                        mma_f16(tmem + (mr * NH + nh) * 256, a_desc + 2 * j + ((mr * kTM * 128) >> 4), b_desc + 2 * j + ((nh * kTNH * 128) >> 4), acc);
             }
             mma_commit(s32(&s_empty[slot]));  // the slot is free again once these MMAs have read it
         }
@@ -221,15 +496,16 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     }
 
     if (warp < 4) {
-        // ---- epilogue: thread = weight row (TMEM lane), 16 loads of 32 columns
+        // ---- epilogue: thread = weight row (TMEM lane) of each row half, loads of 32 columns
         const bool ok = bar_wait(s32(&s_done), 0, failed);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int row = row0 + threadIdx.x;
         if (ok) {
 #pragma unroll 1
-            for (int c = 0; c < kTN / 32; ++c) {
+            for (int cc = 0; cc < MR * (kTN / 32); ++cc) {
+                const int mr = cc / (kTN / 32), c = cc % (kTN / 32);
+                const int row = row0 + mr * kTM + threadIdx.x;
                 uint32_t v[32];
-                const uint32_t at = tmem + (static_cast<uint32_t>(warp * 32) << 16) + c * 32;
+                const uint32_t at = tmem + (static_cast<uint32_t>(warp * 32) << 16) + mr * kTN + c * 32;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
                     "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -258,24 +534,39 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     }
 }
 
-template <int TYPE>
-cudaError_t launch_t(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
-                     unsigned *status, cudaStream_t stream) {
-    constexpr size_t smem = (grid_bytes(TYPE) > 0 ? (grid_bytes(TYPE) + 15) / 16 * 16 : 16) + 1024 + static_cast<size_t>(kTStages) * kTStage;
+template <int TYPE, int MR, int NH>
+cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
+                         unsigned *status, cudaStream_t stream) {
+    constexpr size_t smem = tc5_smem_bytes(TYPE, MR, NH);
+    static_assert(smem <= 227 * 1024, "shared memory of the tcgen05 GEMM");
     static bool configured = false;
     if (!configured) {
-        const cudaError_t err = cudaFuncSetAttribute(qgemm_tc5_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        const cudaError_t err =
+            cudaFuncSetAttribute(qgemm_tc5_kernel<TYPE, MR, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess) return err;
         configured = true;
     }
-    const dim3 grid((rows + kTM - 1) / kTM, (ntok + kTN - 1) / kTN);
-    qgemm_tc5_kernel<TYPE><<<grid, kTThreads, smem, stream>>>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status);
+    const dim3 grid((rows + kTM * MR - 1) / (kTM * MR), (ntok + kTNH * NH - 1) / (kTNH * NH));
+    qgemm_tc5_kernel<TYPE, MR, NH><<<grid, kTThreads, smem, stream>>>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status);
     return cudaGetLastError();
+}
+
+template <int TYPE>
+cudaError_t launch_t(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
+                     unsigned *status, cudaStream_t stream) {
+    if (ntok <= kTNH) return launch_shape<TYPE, 1, 1>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+    // 256 weight rows per block decode every weight once per 256 activation rows instead of once per 512: only worth it with
+    // a fast decoder (measured for Q3_K with the generic one: 187 us instead of 172)
+    if constexpr (fits_two_row_halves(TYPE) && has_fast_chunk(TYPE)) {
+        return launch_shape<TYPE, 2, 1>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+    } else {
+        return launch_shape<TYPE, 1, 2>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+    }
 }
 
 }  // namespace
 
-int gemm_tc5_token_tile() { return kTN; }
+int gemm_tc5_token_tile() { return 2 * kTNH; }  // the activation buffer is padded to the largest tile
 bool gemm_tc5_supports(int cols) { return cols % kTK == 0; }
 
 cudaError_t launch_qgemm_tc5(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
