@@ -18,8 +18,9 @@
 //   * one thread of warp 19 issues, per slot, 2 K-steps x the accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
 //     K = 16) from shared-memory descriptors and commits them to the slot's "empty" mbarrier, which hands the slot
 //     back to the producers, so tile production runs up to three slots ahead of the MMAs;
-//   * after the last commit, warps 0-3 read the accumulators with tcgen05.ld (warp w owns lanes 32w..32w+31, one
-//     weight row per thread and row half) and store y; a warp stores 32 consecutive rows of one activation row, 128 bytes.
+//   * after the last commit, warps 0-15 read the accumulators with tcgen05.ld (warp w reads lanes 32 (w % 4) onwards, one
+//     weight row per thread and row half; the four warps of a lane group share the columns) and store y; a warp stores 32
+//     consecutive rows of one activation row, 128 bytes.
 // Where the time goes (Q4_K 17408 x 5120, 512 activation rows, 141 us with the activation conversion; experiment builds
 // with VQM_TC5_ABLATE): the MMA issue loop alone, never waiting, 81 us (640 MMAs of 128 x 256 x 16 at about 1.7 GHz are
 // 50 us; the rest is the conversion kernel, the prologue and the epilogue that nothing overlaps); with the barriers but
@@ -495,17 +496,19 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
         mma_commit(s32(&s_done));
     }
 
-    if (warp < 4) {
-        // ---- epilogue: thread = weight row (TMEM lane) of each row half, loads of 32 columns
+    if (warp < 16) {
+        // ---- epilogue: thread = weight row (TMEM lane) of each row half, loads of 32 columns.  A warp may read the 32 lanes
+        //      (warp % 4) * 32 onwards, so the sixteen decoder warps work as four groups that share the column chunks.
         const bool ok = bar_wait(s32(&s_done), 0, failed);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int lane_group = warp & 3, col_group = warp >> 2;
         if (ok) {
 #pragma unroll 1
-            for (int cc = 0; cc < MR * (kTN / 32); ++cc) {
+            for (int cc = col_group; cc < MR * (kTN / 32); cc += 4) {
                 const int mr = cc / (kTN / 32), c = cc % (kTN / 32);
-                const int row = row0 + mr * kTM + threadIdx.x;
+                const int row = row0 + mr * kTM + lane_group * 32 + lane;
                 uint32_t v[32];
-                const uint32_t at = tmem + (static_cast<uint32_t>(warp * 32) << 16) + mr * kTN + c * 32;
+                const uint32_t at = tmem + (static_cast<uint32_t>(lane_group * 32) << 16) + mr * kTN + c * 32;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
                     "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
