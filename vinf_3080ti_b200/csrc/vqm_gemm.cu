@@ -23,9 +23,27 @@ namespace {
 constexpr int kBM = 64, kBN = 256, kBK = 32, kLd = kBK + 8;  // +8 halves: conflict-free ldmatrix rows
 constexpr int kGemmThreads = 256;
 
+// The GEMM that follows is launched with programmatic stream serialization: its blocks may set themselves up while this
+// kernel still runs (they wait for its completion before they read xh), so the trigger comes first.
 __global__ void __launch_bounds__(256) f32_to_f16_rows_kernel(const float *x, __half *xh, long long n_valid, long long n_total) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n_total) xh[i] = __float2half_rn(i < n_valid ? x[i] : 0.0f);
+}
+// Eight elements per thread: two 16-byte loads, one 16-byte store (x 16-byte aligned, both counts multiples of 8).
+__global__ void __launch_bounds__(256) f32_to_f16_rows8_kernel(const float4 *x, uint4 *xh, long long n_valid8, long long n_total8) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_total8) return;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (i < n_valid8) {
+        const float4 a = x[2 * i], b = x[2 * i + 1];
+        const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w), h2 = __floats2half2_rn(b.x, b.y),
+                      h3 = __floats2half2_rn(b.z, b.w);
+        out = make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
+                         *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
+    }
+    xh[i] = out;
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
@@ -165,8 +183,14 @@ cudaError_t launch_t(const uint8_t *w, const __half *xh, float *y, int rows, int
 int gemm_token_tile() { return kBN; }
 
 cudaError_t launch_f32_to_f16_rows(const float *x, void *xh, long long n_valid, long long n_total, cudaStream_t stream) {
-    const long long blocks = (n_total + 255) / 256;
-    f32_to_f16_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, static_cast<__half *>(xh), n_valid, n_total);
+    if (n_valid % 8 == 0 && n_total % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(xh) % 16 == 0) {
+        const long long blocks = (n_total / 8 + 255) / 256;
+        f32_to_f16_rows8_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(reinterpret_cast<const float4 *>(x), static_cast<uint4 *>(xh),
+                                                                                   n_valid / 8, n_total / 8);
+    } else {
+        const long long blocks = (n_total + 255) / 256;
+        f32_to_f16_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, static_cast<__half *>(xh), n_valid, n_total);
+    }
     return cudaGetLastError();
 }
 

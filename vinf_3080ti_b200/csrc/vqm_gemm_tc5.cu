@@ -156,7 +156,7 @@ template <int N>
 struct Int {
     static constexpr int value = N;
 };
-__host__ __device__ constexpr bool has_fast_chunk(int type) { return type == kQ4_K || type == kQ5_K; }
+__host__ __device__ constexpr bool has_fast_chunk(int type) { return type == kQ4_K || type == kQ5_K || type == kQ6_K || type == kQ3_K; }
 
 __device__ __forceinline__ uint32_t f16x2_of(f32x2 v) {  // (lo, hi) -> two fp16 in one word, round to nearest even
     float lo, hi;
@@ -215,6 +215,95 @@ template <>
 struct FastHeader<kQ4_K> : FastHeaderK45<kQ4_K> {};
 template <>
 struct FastHeader<kQ5_K> : FastHeaderK45<kQ5_K> {};
+// Eight bytes at a 2-byte aligned shared address: three aligned words and two funnel shifts.
+__device__ __forceinline__ void lds64_a2(uint32_t a, uint32_t &lo, uint32_t &hi) {
+    const uint32_t b = a & ~3u, sh = (a & 2u) * 8u;
+    const uint32_t w0 = lds32(b), w1 = lds32(b + 4), w2 = lds32(b + 8);
+    lo = __funnelshift_r(w0, w1, sh);
+    hi = __funnelshift_r(w1, w2, sh);
+}
+// the four bytes of `w` (minus the bias inside neg_magic) times dl (packed), as fp16
+__device__ __forceinline__ void bytes_mul_f16(uint32_t w, f32x2 neg_magic, f32x2 dl, uint32_t &h0, uint32_t &h1) {
+    h0 = f16x2_of(mul2(bytes_to_pair<0, 1>(w, neg_magic), dl));
+    h1 = f16x2_of(mul2(bytes_to_pair<2, 3>(w, neg_magic), dl));
+}
+
+// Q6_K (engine/csrc/common/qwen_quant.cuh:197-212): low nibbles @0 (128), high 2 bits @128 (64), int8 scales @192 (16),
+// d @208; weight = d * sc * (q - 32).  Chunk c = 4 G + quarter of the block: low nibbles at 64 (G / 4) + 32 (G % 2) +
+// 8 quarter, nibble (G % 4) / 2; high bits at 128 + 32 (G / 4) + 8 quarter, bit pair G % 4; scale c / 2.  The thread's six
+// 8-byte fields of the block are loaded once (the blocks are only 2-byte aligned).
+template <>
+struct FastHeader<kQ6_K> {
+    uint32_t ql[4][2], qh[2][2];  // [G / 4 * 2 + G % 2], [G / 4]
+    uint32_t sc[2];               // the thread's eight scales (slots 0..3, 4..7), one per byte, as int8 + 128
+    float d;
+    __device__ __forceinline__ void load(uint32_t blk, int quarter) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) lds64_a2(blk + (i >> 1) * 64 + (i & 1) * 32 + 8 * quarter, ql[i][0], ql[i][1]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) lds64_a2(blk + 128 + 32 * i + 8 * quarter, qh[i][0], qh[i][1]);
+        uint32_t s0, s1, s2, s3;  // the 16 scales; the thread's are the even or the odd bytes
+        lds64_a2(blk + 192, s0, s1);
+        lds64_a2(blk + 200, s2, s3);
+        const uint32_t sel = (quarter >> 1) ? 0x7531u : 0x6420u;
+        sc[0] = __byte_perm(s0, s1, sel) ^ 0x80808080u;
+        sc[1] = __byte_perm(s2, s3, sel) ^ 0x80808080u;
+        d = half_bits_to_float(lds16(blk + 208));
+    }
+    template <int G>
+    __device__ __forceinline__ void chunk(uint32_t, int, uint32_t (&h)[4]) const {
+        const float dl = d * byte_to_float<G & 3>(sc[G >> 2], 128.0f);
+        constexpr int LS = ((G & 3) >> 1) * 4, HS = 2 * (G & 3);
+        uint32_t w[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t lo = ql[(G >> 2) * 2 + (G & 1)][i], hi = qh[G >> 2][i];
+            w[i] = ((lo >> LS) & 0x0F0F0F0Fu) | ((HS <= 4 ? hi << (4 - HS) : hi >> (HS - 4)) & 0x30303030u);
+        }
+        const f32x2 neg_magic = pack2(-(8388608.0f + 32.0f), -(8388608.0f + 32.0f)), dl2 = pack2(dl, dl);
+        bytes_mul_f16(w[0], neg_magic, dl2, h[0], h[1]);
+        bytes_mul_f16(w[1], neg_magic, dl2, h[2], h[3]);
+    }
+};
+
+// Q3_K (engine/csrc/common/qwen_quant.cuh:225-246): high-bit mask @0 (32), 2-bit quants @32 (64), 12 bytes of 6-bit
+// scales @96, d @108; weight = d * (sc - 32) * ((q2 | hbit << 2) - 4).  Chunk c = 4 G + quarter: quants at 32 + 32 (G / 4) +
+// 8 quarter, bit pair G % 4; mask at 8 quarter, bit G; scale c / 2.
+template <>
+struct FastHeader<kQ3_K> {
+    uint32_t hm[2], qs[2][2];
+    uint32_t sc[4];  // sc[G / 2]: the scale of slot G in byte 2 (G % 2), as the 6-bit field (32 too large)
+    float d;
+    __device__ __forceinline__ void load(uint32_t blk, int quarter) {
+        lds64_a2(blk + 8 * quarter, hm[0], hm[1]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) lds64_a2(blk + 32 + 32 * i + 8 * quarter, qs[i][0], qs[i][1]);
+        uint32_t s0, s1;
+        lds64_a2(blk + 96, s0, s1);
+        const uint32_t s2 = lds32_a2(blk + 104);
+        d = half_bits_to_float(lds16(blk + 108));
+        // scales k = 0..15, four per word: low nibbles of bytes 0..7 (k < 8) or their high nibbles, two more bits from
+        // byte 8 + k % 4 at bit pair k / 4
+        const uint32_t k0 = (s0 & 0x0F0F0F0Fu) | ((s2 << 4) & 0x30303030u), k1 = (s1 & 0x0F0F0F0Fu) | ((s2 << 2) & 0x30303030u);
+        const uint32_t k2 = ((s0 >> 4) & 0x0F0F0F0Fu) | (s2 & 0x30303030u), k3 = ((s1 >> 4) & 0x0F0F0F0Fu) | ((s2 >> 2) & 0x30303030u);
+        // the thread's scale of slot G is k = 2 G + quarter / 2: byte 2 (G % 2) + quarter / 2 of word G / 2
+        const uint32_t sh = (quarter >> 1) * 8;
+        sc[0] = k0 >> sh, sc[1] = k1 >> sh, sc[2] = k2 >> sh, sc[3] = k3 >> sh;
+    }
+    template <int G>
+    __device__ __forceinline__ void chunk(uint32_t, int, uint32_t (&h)[4]) const {
+        const float dl = d * byte_to_float<2 * (G & 1)>(sc[G >> 1], 32.0f);
+        constexpr int QS = 2 * (G & 3);
+        uint32_t w[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            w[i] = ((qs[G >> 2][i] >> QS) & 0x03030303u) | ((G <= 2 ? hm[i] << (2 - G) : hm[i] >> (G - 2)) & 0x04040404u);
+        const f32x2 neg_magic = pack2(-(8388608.0f + 4.0f), -(8388608.0f + 4.0f)), dl2 = pack2(dl, dl);
+        bytes_mul_f16(w[0], neg_magic, dl2, h[0], h[1]);
+        bytes_mul_f16(w[1], neg_magic, dl2, h[2], h[3]);
+    }
+};
+
 // (types without a fast decoder never instantiate this)
 template <int TYPE>
 struct FastHeader {
@@ -437,6 +526,9 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
         // ---- activation half-tile: 512 rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist and are zero.
         //      The copies of up to three slots are in flight per thread (one cp.async group per slot).
         const int b = threadIdx.x - kAThreads;
+        // The kernel is launched while the conversion of the activations may still run (programmatic stream
+        // serialization); these warps are the only readers of its output.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         int issued = 0;
         bool alive = true;
         auto issue = [&]() {  // copies of slot `issued`, once the MMAs that read its previous contents are done
@@ -549,9 +641,19 @@ cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows,
         if (err != cudaSuccess) return err;
         configured = true;
     }
-    const dim3 grid((rows + kTM * MR - 1) / (kTM * MR), (ntok + kTNH * NH - 1) / (kTNH * NH));
-    qgemm_tc5_kernel<TYPE, MR, NH><<<grid, kTThreads, smem, stream>>>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((rows + kTM * MR - 1) / (kTM * MR), (ntok + kTNH * NH - 1) / (kTNH * NH));
+    cfg.blockDim = dim3(kTThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    // May start while the kernel before it in the stream (the fp32 -> fp16 conversion of the activations) still runs: the
+    // set-up, the first weight copies and the first decoded tiles overlap it; the activation loaders wait for it.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, qgemm_tc5_kernel<TYPE, MR, NH>, w, xh, y, rows, cols, row_bytes, ntok, codebook, status);
 }
 
 template <int TYPE>

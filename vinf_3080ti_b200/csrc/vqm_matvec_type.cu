@@ -12,7 +12,7 @@ namespace {
 
 // One kernel per (activation rows M, rows per chunk RW).  A warp always decodes RW rows per chunk (rows that do not
 // exist are computed and dropped), so RW is chosen per launch: the smallest height that covers a warp's share of
-// the rows, up to 8 for one or two activation rows and 4 beyond that (registers, and RW * M <= 32 outputs per warp).
+// the rows, up to 4 (registers, and RW * M <= 32 outputs per warp).
 template <int M, int RW>
 struct Variant {
     static constexpr size_t kSmem = matvec_smem_bytes_for<VQM_TYPE, RW, M>();
@@ -104,19 +104,10 @@ cudaError_t launch_one(const MatvecArgs &args, int sm_count, cudaStream_t stream
     if (a.k_split > 1) return Variant<M, 1>::launch(a, sm_count, stream, grid_out);
     // Taller chunks cost a block per SM (shared memory) and more than they save.  (Two-row chunks at two blocks per SM
     // for more than 4 activation rows were measured too: slower, 106 instead of 74 us for Q4_K 17408 x 5120 at M = 8.)
-    constexpr int kMaxRw = 4;
-    // smallest RW that holds a warp's share; the tallest that can run if the share needs several chunks anyway
+    // smallest RW that holds a warp's share; the tallest (4) if the share needs several chunks anyway
     if (const int n = Variant<M, 1>::rows_per_warp(a.rows, sm_count); n > 0 && n <= 1) return Variant<M, 1>::launch(a, sm_count, stream, grid_out);
     if (const int n = Variant<M, 2>::rows_per_warp(a.rows, sm_count); n > 0 && n <= 2) return Variant<M, 2>::launch(a, sm_count, stream, grid_out);
-    if constexpr (kMaxRw >= 4) {
-        if (const int n = Variant<M, 4>::rows_per_warp(a.rows, sm_count); n > 0 && (n <= 4 || kMaxRw == 4)) return Variant<M, 4>::launch(a, sm_count, stream, grid_out);
-    }
-    if constexpr (kMaxRw == 8) {
-        if (Variant<M, 8>::blocks_per_sm() > 0) return Variant<M, 8>::launch(a, sm_count, stream, grid_out);
-    }
-    if constexpr (kMaxRw >= 4) {
-        if (Variant<M, 4>::blocks_per_sm() > 0) return Variant<M, 4>::launch(a, sm_count, stream, grid_out);
-    }
+    if (Variant<M, 4>::blocks_per_sm() > 0) return Variant<M, 4>::launch(a, sm_count, stream, grid_out);
     if (Variant<M, 2>::blocks_per_sm() > 0) return Variant<M, 2>::launch(a, sm_count, stream, grid_out);
     return Variant<M, 1>::launch(a, sm_count, stream, grid_out);
 }
