@@ -375,7 +375,10 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
         // ---- weight half-tile: four threads per row, one chunk each; chunk c of the stage (8 weights, 16 bytes of fp16)
         //      goes to 16-byte slot c ^ (row % 8) of the row
         //      (the four threads of a row are neighbours in a warp: their global loads fall into the same sectors)
-        const int r = threadIdx.x >> 2, quarter = threadIdx.x & 3;  // rows r + 128 * mr of the block
+        // rows r + 128 * mr of the block; the rows of a warp go 0, 4, 1, 5, ...: the 8 lanes the store unit serves together
+        // then hit 8 different 16-byte columns of the swizzle (rows r and r + 4 use opposite halves)
+        const int quarter = threadIdx.x & 3, r8 = (threadIdx.x >> 2) & 7;
+        const int r = (threadIdx.x >> 5) * 8 + ((r8 >> 1) | ((r8 & 1) << 2));
         bool valid[MR];
         const uint8_t *w_row[MR];
 #pragma unroll
@@ -544,7 +547,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 #else
             for (int i = b; i < kTN * 4; i += kBThreads) {
 #endif
-                const int n = i >> 2, c = (slot & 1) * 4 + (i & 3);
+                const int n = i >> 2, c = (slot & 1) * 4 + (i & 3);  // (the decoder warps' row order was tried here: slower)
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_tile + n * 128 + ((c ^ (n & 7)) << 4)),
                              "l"(src + static_cast<size_t>(n) * cols + (i & 3) * 8)
                              : "memory");
