@@ -124,13 +124,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
     return ok != 0;
 }
 
-// Bounded wait: at most 2^18 polls of up to ~20 microseconds each (a few seconds: longer than the bounded wait for another
-// rank's push, which comes first in a kernel and must be the one that reports), then the caller reports the expiry.
+// Both kinds of bounded wait measure their limit in time (the global nanosecond timer), not in polls: how long a poll takes
+// varies by orders of magnitude (the suspend-time hint is only an upper bound), and the order of the two limits matters -
+// the wait for another rank's push comes first in a kernel, has the shorter limit and must be the one that reports.
+constexpr unsigned long long kPeerWaitNs = 1000000000ull;   // 1 s
+constexpr unsigned long long kMbarWaitNs = 4000000000ull;   // 4 s
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait on an mbarrier: polls of up to ~20 microseconds each until kMbarWaitNs have passed (and at most 2^26 polls,
+// whatever the timer says), then the caller reports the expiry.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity, 2000u)) return true;
+    const unsigned long long t0 = global_ns();
 #pragma unroll 1
-    for (int i = 0; i < (1 << 18); ++i)
+    for (int i = 0; i < (1 << 26); ++i) {
         if (mbar_try_wait(bar, parity, 20000u)) return true;
+        if ((i & 63) == 63 && global_ns() - t0 > kMbarWaitNs) break;
+    }
     return false;
 }
 
@@ -349,8 +363,11 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
                 return v;
             };
+            unsigned long long t0 = 0;
             while (static_cast<int>(acquire(flag) - target) < 0) {
-                if (++spins > (1 << 22)) {
+                ++spins;
+                if (spins == 64) t0 = global_ns();  // a push that is merely in flight is seen long before this
+                if ((spins > 64 && (spins & 255) == 0 && global_ns() - t0 > kPeerWaitNs) || spins > (1 << 26)) {
                     ok = false;
                     break;
                 }
