@@ -48,10 +48,10 @@ namespace {
 //               (Q4_K): 256 weight rows per block halve what the blocks together pull out of L2 for the activations
 //               (every block reads its activation tile once per weight tile: 713 MB for 17408 x 5120 x 512);
 //   MR 1, NH 2  more than that, for the other types.
-constexpr int kTM = 128, kTNH = 256, kTK = 64, kTStages = 2;
+constexpr int kTM = 128, kTNH = 256, kTK = 64;
+constexpr int kMaxStages = 4;  // stages of the tile ring: as many as fit into shared memory, see stages_for
 constexpr int kTA1 = kTM * kTK * 2, kTB1 = kTNH * kTK * 2;  // 16 KB per 128 weight rows, 32 KB per 256 activation rows
 __host__ __device__ constexpr int stage_bytes(int mr, int nh) { return mr * kTA1 + nh * kTB1; }
-constexpr int kTSlots = 2 * kTStages;  // half stages
 constexpr int kTThreads = 640;
 constexpr int kAThreads = 512, kBThreads = 96;
 // Raw-block ring: a "column" is 256 weight columns of the 128 rows; a row's bytes of one column are contiguous.
@@ -63,11 +63,18 @@ __host__ __device__ constexpr int raw_slot_bytes(int type) { return (raw_run_byt
 __host__ __device__ constexpr bool raw_staged(int type) { return raw_run_bytes(type) <= 210; }  // every type up to Q6_K; not Q8_0, F16, F32 (the ring would not fit)
 __host__ __device__ constexpr int raw_ring_bytes(int type, int mr) { return raw_staged(type) ? 2 * mr * kTM * raw_slot_bytes(type) : 0; }
 __host__ __device__ constexpr int table_bytes16(int type) { return grid_bytes(type) > 0 ? (grid_bytes(type) + 15) / 16 * 16 : 16; }
-__host__ __device__ constexpr size_t tc5_smem_bytes(int type, int mr, int nh) {
-    return table_bytes16(type) + 1024 + static_cast<size_t>(kTStages) * stage_bytes(mr, nh) + raw_ring_bytes(type, mr);
+__host__ __device__ constexpr size_t tc5_smem_bytes(int type, int mr, int nh, int stages) {
+    return table_bytes16(type) + 1024 + static_cast<size_t>(stages) * stage_bytes(mr, nh) + raw_ring_bytes(type, mr);
+}
+// The ring is what hides the refill round trip of a slot (MMAs done -> "empty" -> copies from L2 / decode -> "full"),
+// which is several times longer than a slot's MMAs: every stage that fits is used.
+__host__ __device__ constexpr int stages_for(int type, int mr, int nh) {
+    int s = kMaxStages;
+    while (s > 2 && tc5_smem_bytes(type, mr, nh, s) > 227 * 1024) --s;
+    return s;
 }
 // 256 weight rows per block need the raw ring for 256 rows (reading them from global memory per chunk is too slow there)
-__host__ __device__ constexpr bool fits_two_row_halves(int type) { return raw_staged(type) && tc5_smem_bytes(type, 2, 1) <= 227 * 1024; }
+__host__ __device__ constexpr bool fits_two_row_halves(int type) { return raw_staged(type) && tc5_smem_bytes(type, 2, 1, 2) <= 227 * 1024; }
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -307,10 +314,11 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     constexpr int CPB = chunk_block(TYPE) / 8, BB = chunk_block_bytes(TYPE);
     constexpr int TABLE = table_bytes16(TYPE);
     constexpr int kTStage = stage_bytes(MR, NH), kTA = MR * kTA1, kTN = NH * kTNH;
+    constexpr int kTStages = stages_for(TYPE, MR, NH), kTSlots = 2 * kTStages;  // slots: half stages
     constexpr uint32_t kTmemCols = 256 * MR * NH;
     static_assert(MR * NH <= 2, "512 columns of tensor memory");
     extern __shared__ uint8_t tc5_raw[];
-    __shared__ __align__(8) uint64_t s_full[kTSlots], s_empty[kTSlots], s_done, s_raw_full[2], s_raw_empty[2];
+    __shared__ __align__(8) uint64_t s_full[2 * kMaxStages], s_empty[2 * kMaxStages], s_done, s_raw_full[2], s_raw_empty[2];
     __shared__ uint32_t s_tmem;
     __shared__ int s_failed;
     // table first, then the stages on a 1024-byte boundary (the swizzle works on absolute shared-memory address bits)
@@ -543,13 +551,19 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
             asm volatile("cp.async.commit_group;" ::: "memory");
             ++issued;
         };
-        while (alive && issued < n_slots && issued < 3) issue();
+        constexpr int kWindow = kTSlots - 1;  // slots whose copies are in flight per thread
+        while (alive && issued < n_slots && issued < kWindow) issue();
         for (int q = 0; alive && q < n_slots; ++q) {
             // groups complete in order: slot q has landed once at most (issued - q - 1) groups are still pending
-            const int pending = issued - q - 1;
-            if (pending >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
-            else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
-            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            switch (issued - q - 1) {
+                case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+                case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+                case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+                case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+                case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+                case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+                default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             warp_arrive(s32(&s_full[q % kTSlots]));
             if (issued < n_slots) issue();
@@ -623,7 +637,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 template <int TYPE, int MR, int NH>
 cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
                          unsigned *status, cudaStream_t stream) {
-    constexpr size_t smem = tc5_smem_bytes(TYPE, MR, NH);
+    constexpr size_t smem = tc5_smem_bytes(TYPE, MR, NH, stages_for(TYPE, MR, NH));
     static_assert(smem <= 227 * 1024, "shared memory of the tcgen05 GEMM");
     static bool configured = false;
     if (!configured) {
