@@ -5,6 +5,11 @@
 //   * a block owns 128 or 256 weight rows (one or two MMA M-halves) and 256 or 512 activation rows, as one or two
 //     accumulators of 128 x 256 fp32 in tensor memory (at most 512 columns, the whole TMEM of an SM: one block per SM);
 //     the shapes and when each is used are listed at stage_bytes below;
+//   * two blocks of a cluster can work as a pair (tcgen05.mma.cta_group::2, M = 256): each decodes its own 128 weight rows
+//     per accumulator and holds half of the accumulator's 256 activation rows in its shared memory, which halves what a
+//     block reads of the activations from L2; the first block issues the MMAs for both and commits to the barriers of
+//     both (multicast commit), the second block forwards its "full" slots to the first with one remote arrive per slot,
+//     each block drains its own 128 lanes of tensor memory;
 //   * the raw weight bytes come in by bulk copies (1-D TMA, no multicast), 256 columns of the block's rows at a time
 //     into a ring of two shared-memory buffers, one copy per row issued by the row's first decoder thread, so that the
 //     decoders never wait for global memory (types whose 256 columns are too wide for the ring - Q8_0, F16, F32 - are
@@ -42,16 +47,18 @@ namespace vqm {
 namespace {
 
 // A block computes kTM * MR weight rows by kTNH * NH activation rows: MR x NH accumulators of 128 x 256 in tensor memory
-// (MR * NH <= 2: 512 columns).  The three shapes in use:
-//   MR 1, NH 1  up to 256 activation rows;
-//   MR 2, NH 1  more than that, for the types with a fast decoder whose raw-block ring for 256 rows fits beside the tiles
-//               (Q4_K): 256 weight rows per block halve what the blocks together pull out of L2 for the activations
-//               (every block reads its activation tile once per weight tile: 713 MB for 17408 x 5120 x 512);
-//   MR 1, NH 2  more than that, for the other types.
+// (MR * NH <= 2: 512 columns).  Shapes in use: 1 x 1, 2 x 1 (256 weight rows per block halve what the blocks together pull
+// out of L2 for the activations - every block reads its activation tile once per weight tile, 713 MB for 17408 x 5120 x
+// 512 at 1 x 2 - at the price of decoding every weight once per 256 instead of 512 activation rows), 1 x 2; alone or as a
+// pair of blocks (see stage_bytes).  launch_t picks.
 constexpr int kTM = 128, kTNH = 256, kTK = 64;
 constexpr int kMaxStages = 4;  // stages of the tile ring: as many as fit into shared memory, see stages_for
 constexpr int kTA1 = kTM * kTK * 2, kTB1 = kTNH * kTK * 2;  // 16 KB per 128 weight rows, 32 KB per 256 activation rows
-__host__ __device__ constexpr int stage_bytes(int mr, int nh) { return mr * kTA1 + nh * kTB1; }
+// With PAIR two blocks of a cluster (two SMs) work as one: tcgen05.mma.cta_group::2 multiplies the 256 weight rows of the
+// two blocks (128 each, M = 256) by 256 activation rows of which each block holds one half in its shared memory, so a
+// block pulls only half of the activation tile out of L2 - the traffic that bounds this kernel.  Accumulator rows stay
+// with the block that decoded them (its 128 lanes of tensor memory).
+__host__ __device__ constexpr int stage_bytes(int mr, int nh, bool pair) { return mr * kTA1 + nh * (pair ? kTB1 / 2 : kTB1); }
 constexpr int kTThreads = 640;
 constexpr int kAThreads = 512, kBThreads = 96;
 // Raw-block ring: a "column" is 256 weight columns of the 128 rows; a row's bytes of one column are contiguous.
@@ -63,18 +70,18 @@ __host__ __device__ constexpr int raw_slot_bytes(int type) { return (raw_run_byt
 __host__ __device__ constexpr bool raw_staged(int type) { return raw_run_bytes(type) <= 210; }  // every type up to Q6_K; not Q8_0, F16, F32 (the ring would not fit)
 __host__ __device__ constexpr int raw_ring_bytes(int type, int mr) { return raw_staged(type) ? 2 * mr * kTM * raw_slot_bytes(type) : 0; }
 __host__ __device__ constexpr int table_bytes16(int type) { return grid_bytes(type) > 0 ? (grid_bytes(type) + 15) / 16 * 16 : 16; }
-__host__ __device__ constexpr size_t tc5_smem_bytes(int type, int mr, int nh, int stages) {
-    return table_bytes16(type) + 1024 + static_cast<size_t>(stages) * stage_bytes(mr, nh) + raw_ring_bytes(type, mr);
+__host__ __device__ constexpr size_t tc5_smem_bytes(int type, int mr, int nh, bool pair, int stages) {
+    return table_bytes16(type) + 1024 + static_cast<size_t>(stages) * stage_bytes(mr, nh, pair) + raw_ring_bytes(type, mr);
 }
 // The ring is what hides the refill round trip of a slot (MMAs done -> "empty" -> copies from L2 / decode -> "full"),
 // which is several times longer than a slot's MMAs: every stage that fits is used.
-__host__ __device__ constexpr int stages_for(int type, int mr, int nh) {
+__host__ __device__ constexpr int stages_for(int type, int mr, int nh, bool pair) {
     int s = kMaxStages;
-    while (s > 2 && tc5_smem_bytes(type, mr, nh, s) > 227 * 1024) --s;
+    while (s > 2 && tc5_smem_bytes(type, mr, nh, pair, s) > 227 * 1024) --s;
     return s;
 }
 // 256 weight rows per block need the raw ring for 256 rows (reading them from global memory per chunk is too slow there)
-__host__ __device__ constexpr bool fits_two_row_halves(int type) { return raw_staged(type) && tc5_smem_bytes(type, 2, 1, 2) <= 227 * 1024; }
+__host__ __device__ constexpr bool fits_two_row_halves(int type, bool pair) { return raw_staged(type) && tc5_smem_bytes(type, 2, 1, pair, 2) <= 227 * 1024; }
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -95,6 +102,18 @@ __device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait that acquires at cluster scope: pairs with the other block's arrive of cluster scope
+__device__ __forceinline__ bool bar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait; also gives up as soon as another thread of the block has (`failed` is a shared flag).
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int *failed) {
 #pragma unroll 1
@@ -103,6 +122,16 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile
         if (bar_try(bar, parity)) return true;
         if (*failed) return false;
         if (i > 4096) __nanosleep(200);  // only a wait that is already far beyond a pipeline step backs off
+    }
+    *failed = 1;
+    return false;
+}
+__device__ __forceinline__ bool bar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *failed) {
+#pragma unroll 1
+    for (int i = 0; i < (1 << 22); ++i) {
+        if (bar_try_cluster(bar, parity)) return true;
+        if (*failed) return false;
+        if (i > 4096) __nanosleep(200);
     }
     *failed = 1;
     return false;
@@ -307,14 +336,52 @@ struct FastHeader {
     __device__ __forceinline__ void chunk(uint32_t, int, uint32_t (&)[4]) const {}
 };
 
-template <int TYPE, int MR, int NH>
+// ---- the two blocks of a pair ----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the address, in the cluster's shared window, of the same variable in block `rank`
+__device__ __forceinline__ uint32_t in_block(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_addr) {
+    // default semantics, as for a consumer's release of a remote slot; with .release.cluster every slot took 0.2 us longer
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Instruction descriptor of the pair MMA: M = 256 (128 rows from each block), N = 256.
+constexpr uint32_t kIdescPair = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdescPair), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at this address in both blocks of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(both)
+                 : "memory");
+}
+
+template <int TYPE, int MR, int NH, bool PAIR>
 __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *w, const __half *xh, float *y, int rows, int cols,
                                                                  long long row_bytes, int ntok, const uint8_t *codebook,
                                                                  unsigned *status) {
     constexpr int CPB = chunk_block(TYPE) / 8, BB = chunk_block_bytes(TYPE);
     constexpr int TABLE = table_bytes16(TYPE);
-    constexpr int kTStage = stage_bytes(MR, NH), kTA = MR * kTA1, kTN = NH * kTNH;
-    constexpr int kTStages = stages_for(TYPE, MR, NH), kTSlots = 2 * kTStages;  // slots: half stages
+    constexpr int kTStage = stage_bytes(MR, NH, PAIR), kTA = MR * kTA1, kTN = NH * kTNH;
+    constexpr int kBN = PAIR ? kTNH / 2 : kTNH;       // activation rows of an accumulator's tile that this block holds
+    constexpr int kRowsPerAcc = PAIR ? 2 * kTM : kTM;  // weight rows of an accumulator (both blocks of a pair)
+    constexpr int kTStages = stages_for(TYPE, MR, NH, PAIR), kTSlots = 2 * kTStages;  // slots: half stages
     constexpr uint32_t kTmemCols = 256 * MR * NH;
     static_assert(MR * NH <= 2, "512 columns of tensor memory");
     extern __shared__ uint8_t tc5_raw[];
@@ -328,12 +395,16 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     constexpr int RSLOT = raw_slot_bytes(TYPE), RUN = raw_run_bytes(TYPE);
     const uint32_t raw_ring = tiles + kTStages * kTStage;  // two buffers of MR * kTM row slots
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * (kTM * MR), tok0 = blockIdx.y * kTN;
+    // a pair is two consecutive blocks of the grid's x; block `rank` of it owns rows rank * 128 .. + 127 of each accumulator
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;
+    const int row0 = static_cast<int>(PAIR ? blockIdx.x >> 1 : blockIdx.x) * (kRowsPerAcc * MR) + static_cast<int>(rank) * kTM;
+    const int tok0 = blockIdx.y * kTN;
     const int n_k = cols / kTK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTSlots; ++s) {
-            bar_init(s32(&s_full[s]), (kAThreads + kBThreads) / 32);  // one arrive per producer / loader warp
+            // one arrive per producer / loader warp, and in the first block of a pair one more for the second block's slot
+            bar_init(s32(&s_full[s]), (kAThreads + kBThreads) / 32 + ((PAIR && rank == 0) ? 1 : 0));
             bar_init(s32(&s_empty[s]), 1);
         }
         bar_init(s32(&s_done), 1);
@@ -353,14 +424,24 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
         }
     }
     if (warp == 0) {  // tensor memory: 256 columns per accumulator (one block per SM)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&s_tmem)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&s_tmem)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&s_tmem)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // the other block's barriers and tensor memory exist before anybody signals or multiplies
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
     volatile int *failed = &s_failed;
+    // "full" is counted per block; the second block of a pair forwards each completed slot to the first block, which
+    // issues the MMAs, with one arrive of cluster scope (such an arrive per producer warp made every slot take a
+    // microsecond)
+    auto full_arrive = [&](int slot) { warp_arrive(s32(&s_full[slot])); };
 
     const int n_slots = 2 * n_k;  // slot q of the pipeline: stage (q / 2) % 2, K half q % 2
 #if VQM_TC5_ABLATE & 8
@@ -379,8 +460,8 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
         const uint8_t *w_row[MR];
 #pragma unroll
         for (int mr = 0; mr < MR; ++mr) {
-            valid[mr] = row0 + mr * kTM + r < rows;
-            w_row[mr] = w + static_cast<size_t>(valid[mr] ? row0 + mr * kTM + r : 0) * row_bytes;
+            valid[mr] = row0 + mr * kRowsPerAcc + r < rows;
+            w_row[mr] = w + static_cast<size_t>(valid[mr] ? row0 + mr * kRowsPerAcc + r : 0) * row_bytes;
         }
         // One slot of this thread: wait until the MMAs that read the slot's previous contents are done, store the 8 fp16
         // weights of chunk `quarter` of the half stage for each of its rows (swizzled), make them visible to the tensor
@@ -396,7 +477,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 #if !(VQM_TC5_ABLATE & 4)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 #endif
-            warp_arrive(s32(&s_full[q % kTSlots]));
+            full_arrive(q % kTSlots);
         };
         auto to_f16 = [](const float (&v)[8], uint32_t (&h)[4]) {
 #pragma unroll
@@ -522,8 +603,9 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
             }
         }
     } else if (warp < 19) {
-        // ---- activation half-tile: 512 rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist and are zero.
-        //      The copies of up to three slots are in flight per thread (one cp.async group per slot).
+        // ---- activation half-tile: this block's NH x kBN rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist
+        //      and are zero.  Local row n belongs to accumulator column block n / kBN; in a pair this block holds rows
+        //      rank * kBN .. of each.  The copies of all slots but one are in flight per thread (one cp.async group per slot).
         const int b = threadIdx.x - kAThreads;
         // The kernel is launched while the conversion of the activations may still run (programmatic stream
         // serialization); these warps are the only readers of its output.
@@ -541,11 +623,12 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 #if VQM_TC5_ABLATE & 2
             for (int i = b; i < 0; i += kBThreads) {
 #else
-            for (int i = b; i < kTN * 4; i += kBThreads) {
+            for (int i = b; i < NH * kBN * 4; i += kBThreads) {
 #endif
                 const int n = i >> 2, c = (slot & 1) * 4 + (i & 3);  // (the decoder warps' row order was tried here: slower)
+                const int tok = (n / kBN) * kTNH + static_cast<int>(rank) * kBN + n % kBN;  // within the block's tile of tokens
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_tile + n * 128 + ((c ^ (n & 7)) << 4)),
-                             "l"(src + static_cast<size_t>(n) * cols + (i & 3) * 8)
+                             "l"(src + static_cast<size_t>(tok) * cols + (i & 3) * 8)
                              : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
@@ -565,16 +648,23 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
                 default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            warp_arrive(s32(&s_full[q % kTSlots]));
+            full_arrive(q % kTSlots);
             if (issued < n_slots) issue();
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (lane == 0 && rank != 0) {
+        // ---- second block of a pair: tell the first block about every slot that is full here
+        for (int q = 0; q < n_slots; ++q) {
+            const int slot = q % kTSlots;
+            if (!bar_wait(s32(&s_full[slot]), (q / kTSlots) & 1, failed)) break;
+            bar_arrive_cluster(in_block(s32(&s_full[slot]), 0));
+        }
     } else if (lane == 0) {
-        // ---- MMA issue: accumulator (mr, nh) at column (mr * NH + nh) * 256
+        // ---- MMA issue (the first block of a pair issues for both): accumulator (mr, nh) at column (mr * NH + nh) * 256
         for (int q = 0; q < n_slots; ++q) {
             const int slot = q % kTSlots;
 #if !(VQM_TC5_ABLATE & 8)
-            if (!bar_wait(s32(&s_full[slot]), (q / kTSlots) & 1, failed)) break;
+            if (!(PAIR ? bar_wait_cluster(s32(&s_full[slot]), (q / kTSlots) & 1, failed) : bar_wait(s32(&s_full[slot]), (q / kTSlots) & 1, failed))) break;
 #endif
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t a_desc = sw128_desc(tiles + (slot >> 1) * kTStage), b_desc = sw128_desc(tiles + (slot >> 1) * kTStage + kTA);
@@ -585,12 +675,18 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 #pragma unroll
                 for (int mr = 0; mr < MR; ++mr)
 #pragma unroll
-                    for (int nh = 0; nh < NH; ++nh)  // accumulator (mr, nh): 128 weight rows x 256 activation rows
-                        mma_f16(tmem + (mr * NH + nh) * 256, a_desc + 2 * j + ((mr * kTM * 128) >> 4), b_desc + 2 * j + ((nh * kTNH * 128) >> 4), acc);
+                    for (int nh = 0; nh < NH; ++nh) {  // accumulator (mr, nh): 128 weight rows (per block) x 256 activation rows
+                        const uint64_t a = a_desc + 2 * j + ((mr * kTM * 128) >> 4), bd = b_desc + 2 * j + ((nh * kBN * 128) >> 4);
+                        if constexpr (PAIR) mma_f16_pair(tmem + (mr * NH + nh) * 256, a, bd, acc);
+                        else mma_f16(tmem + (mr * NH + nh) * 256, a, bd, acc);
+                    }
             }
-            mma_commit(s32(&s_empty[slot]));  // the slot is free again once these MMAs have read it
+            // the slot is free again, in both blocks of a pair, once these MMAs have read it
+            if constexpr (PAIR) mma_commit_pair(s32(&s_empty[slot]));
+            else mma_commit(s32(&s_empty[slot]));
         }
-        mma_commit(s32(&s_done));
+        if constexpr (PAIR) mma_commit_pair(s32(&s_done));
+        else mma_commit(s32(&s_done));
     }
 
     if (warp < 16) {
@@ -603,7 +699,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 #pragma unroll 1
             for (int cc = col_group; cc < MR * (kTN / 32); cc += 4) {
                 const int mr = cc / (kTN / 32), c = cc % (kTN / 32);
-                const int row = row0 + mr * kTM + lane_group * 32 + lane;
+                const int row = row0 + mr * kRowsPerAcc + lane_group * 32 + lane;
                 uint32_t v[32];
                 const uint32_t at = tmem + (static_cast<uint32_t>(lane_group * 32) << 16) + mr * kTN + c * 32;
                 asm volatile(
@@ -628,49 +724,66 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // neither block's shared or tensor memory goes away under the other
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
         if (lane == 0 && s_failed) atomicExch(status, kStatusWaitExpired);
     }
 }
 
-template <int TYPE, int MR, int NH>
+template <int TYPE, int MR, int NH, bool PAIR>
 cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
                          unsigned *status, cudaStream_t stream) {
-    constexpr size_t smem = tc5_smem_bytes(TYPE, MR, NH, stages_for(TYPE, MR, NH));
+    constexpr size_t smem = tc5_smem_bytes(TYPE, MR, NH, PAIR, stages_for(TYPE, MR, NH, PAIR));
     static_assert(smem <= 227 * 1024, "shared memory of the tcgen05 GEMM");
     static bool configured = false;
     if (!configured) {
         const cudaError_t err =
-            cudaFuncSetAttribute(qgemm_tc5_kernel<TYPE, MR, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            cudaFuncSetAttribute(qgemm_tc5_kernel<TYPE, MR, NH, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess) return err;
         configured = true;
     }
+    constexpr int kRowsPerUnit = kTM * MR * (PAIR ? 2 : 1);  // weight rows of a block, or of a pair of blocks
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((rows + kTM * MR - 1) / (kTM * MR), (ntok + kTNH * NH - 1) / (kTNH * NH));
+    cfg.gridDim = dim3((rows + kRowsPerUnit - 1) / kRowsPerUnit * (PAIR ? 2 : 1), (ntok + kTNH * NH - 1) / (kTNH * NH));
     cfg.blockDim = dim3(kTThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     // May start while the kernel before it in the stream (the fp32 -> fp16 conversion of the activations) still runs: the
     // set-up, the first weight copies and the first decoded tiles overlap it; the activation loaders wait for it.
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    int n_attr = 1;
+    if constexpr (PAIR) {  // the two blocks of a pair form a cluster
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 2;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, qgemm_tc5_kernel<TYPE, MR, NH>, w, xh, y, rows, cols, row_bytes, ntok, codebook, status);
+    cfg.numAttrs = n_attr;
+    return cudaLaunchKernelEx(&cfg, qgemm_tc5_kernel<TYPE, MR, NH, PAIR>, w, xh, y, rows, cols, row_bytes, ntok, codebook, status);
 }
 
 template <int TYPE>
 cudaError_t launch_t(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
                      unsigned *status, cudaStream_t stream) {
-    if (ntok <= kTNH) return launch_shape<TYPE, 1, 1>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
-    // 256 weight rows per block decode every weight once per 256 activation rows instead of once per 512: only worth it with
-    // a fast decoder (measured for Q3_K with the generic one: 187 us instead of 172)
-    if constexpr (fits_two_row_halves(TYPE) && has_fast_chunk(TYPE)) {
-        return launch_shape<TYPE, 2, 1>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+    // Which shape for which case was measured on 17408 x 5120 weights (times with the conversion of the activations):
+    //   up to 256 activation rows: a pair of blocks with one accumulator each (108 us; a single block 113);
+    //   more: 256 weight rows per block pay only with a fast decoder (Q3_K with the generic one: 187 us instead of 172);
+    //   alone where the raw ring for 256 rows fits beside two stages (Q4_K 122 us, Q3_K 126; as a pair 126 / 131), as a pair
+    //   where it only fits beside the pair's smaller stages (Q5_K 131 us; 1 x 2 alone 137); the other types as pairs of
+    //   1 x 2 blocks (Q6_K 132 us, Q8_0 144; alone 141 / 149).
+    if (ntok <= kTNH) return launch_shape<TYPE, 1, 1, true>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+    if constexpr (has_fast_chunk(TYPE) && fits_two_row_halves(TYPE, false)) {
+        return launch_shape<TYPE, 2, 1, false>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+    } else if constexpr (has_fast_chunk(TYPE) && fits_two_row_halves(TYPE, true)) {
+        return launch_shape<TYPE, 2, 1, true>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
     } else {
-        return launch_shape<TYPE, 1, 2>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+        return launch_shape<TYPE, 1, 2, true>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
     }
 }
 
