@@ -354,7 +354,8 @@ def prefill_gemm(rt, torch, stream, dev, peaks: dict) -> dict:
             "TFLOPs": round(flops / ms / 1e9, 1), "frac_of_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4),
             "frac_of_bf16_sustained": round(flops / ms / 1e9 / peaks["bf16_tflops_sustained"], 4) if peaks.get("bf16_tflops_sustained") else None,
             "note": "fp32 activations -> fp16, weights dequantised to fp16 tiles (raw blocks staged in shared memory, per-block decoders), "
-                    "tcgen05 MMA with fp32 accumulators in tensor memory, 256 weight rows x 256 activation rows per block; "
+                    "tcgen05 MMA with fp32 accumulators in tensor memory, 256 weight rows x 256 activation rows per block (other types and "
+                    "smaller passes: pairs of blocks on cta_group::2); "
                     "time includes the fp32 -> fp16 conversion of the activations"}
 
 
