@@ -32,6 +32,7 @@
 // neither decode nor activation copies 103 us; without the activation copies 126 us; without the decode 135 us.
 // Every mbarrier wait is bounded: on expiry the block records a status code, everybody falls through to the end, and
 // the tensor memory is released before the block returns.
+#include <cuda.h>  // CUtensorMap and the driver entry point that encodes one (types only; nothing links against the driver)
 #include <cuda_fp16.h>
 
 #include "vqm_formats.cuh"
@@ -59,8 +60,9 @@ constexpr int kTA1 = kTM * kTK * 2, kTB1 = kTNH * kTK * 2;  // 16 KB per 128 wei
 // block pulls only half of the activation tile out of L2 - the traffic that bounds this kernel.  Accumulator rows stay
 // with the block that decoded them (its 128 lanes of tensor memory).
 __host__ __device__ constexpr int stage_bytes(int mr, int nh, bool pair) { return mr * kTA1 + nh * (pair ? kTB1 / 2 : kTB1); }
-constexpr int kTThreads = 640;
-constexpr int kAThreads = 512, kBThreads = 96;
+constexpr int kAThreads = 512;           // decoder warps 0-15
+constexpr int kTThreads = kAThreads + 64;  // warp 16: one thread feeds the activation tiles (TMA); warp 17: one thread issues the MMAs
+constexpr int kLoadWarp = kAThreads / 32;  // the MMA warp is the one after it
 // Raw-block ring: a "column" is 256 weight columns of the 128 rows; a row's bytes of one column are contiguous.
 constexpr int kRawCols = 256;
 __host__ __device__ constexpr int raw_run_bytes(int type) { return kRawCols / chunk_block(type) * chunk_block_bytes(type); }
@@ -373,8 +375,8 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
 }
 
 template <int TYPE, int MR, int NH, bool PAIR>
-__global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *w, const __half *xh, float *y, int rows, int cols,
-                                                                 long long row_bytes, int ntok, const uint8_t *codebook,
+__global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_t *w, float *y, int rows,
+                                                                 int cols, long long row_bytes, int ntok, const uint8_t *codebook,
                                                                  unsigned *status) {
     constexpr int CPB = chunk_block(TYPE) / 8, BB = chunk_block_bytes(TYPE);
     constexpr int TABLE = table_bytes16(TYPE);
@@ -385,7 +387,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     constexpr uint32_t kTmemCols = 256 * MR * NH;
     static_assert(MR * NH <= 2, "512 columns of tensor memory");
     extern __shared__ uint8_t tc5_raw[];
-    __shared__ __align__(8) uint64_t s_full[2 * kMaxStages], s_empty[2 * kMaxStages], s_done, s_raw_full[2], s_raw_empty[2];
+    __shared__ __align__(8) uint64_t s_full[2 * kMaxStages], s_empty[2 * kMaxStages], s_xfull[kMaxStages], s_done, s_raw_full[2], s_raw_empty[2];
     __shared__ uint32_t s_tmem;
     __shared__ int s_failed;
     // table first, then the stages on a 1024-byte boundary (the swizzle works on absolute shared-memory address bits)
@@ -403,10 +405,11 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTSlots; ++s) {
-            // one arrive per producer / loader warp, and in the first block of a pair one more for the second block's slot
-            bar_init(s32(&s_full[s]), (kAThreads + kBThreads) / 32 + ((PAIR && rank == 0) ? 1 : 0));
+            // one arrive per decoder warp, and in the first block of a pair one more for the second block's slot
+            bar_init(s32(&s_full[s]), kAThreads / 32 + ((PAIR && rank == 0) ? 1 : 0));
             bar_init(s32(&s_empty[s]), 1);
         }
+        for (int s = 0; s < kTStages; ++s) bar_init(s32(&s_xfull[s]), 1);  // the feeding thread's arrive with the stage's byte count
         bar_init(s32(&s_done), 1);
         for (int b = 0; b < 2; ++b) {
             bar_init(s32(&s_raw_full[b]), kTM);         // one arrive (with its byte count) per first thread of a row
@@ -445,7 +448,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
 
     const int n_slots = 2 * n_k;  // slot q of the pipeline: stage (q / 2) % 2, K half q % 2
 #if VQM_TC5_ABLATE & 8
-    if (warp < 19) {
+    if (warp <= kLoadWarp) {
     } else
 #endif
     if (warp < 16) {
@@ -602,61 +605,37 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
                 for (int i = 0; i < (1 << 16) && !bar_try(s32(&s_raw_full[col & 1]), (col >> 1) & 1); ++i) __nanosleep(64);
             }
         }
-    } else if (warp < 19) {
-        // ---- activation half-tile: this block's NH x kBN rows x 4 chunks of 16 bytes, same swizzle; rows beyond ntok exist
-        //      and are zero.  Local row n belongs to accumulator column block n / kBN; in a pair this block holds rows
-        //      rank * kBN .. of each.  The copies of all slots but one are in flight per thread (one cp.async group per slot).
-        const int b = threadIdx.x - kAThreads;
-        // The kernel is launched while the conversion of the activations may still run (programmatic stream
-        // serialization); these warps are the only readers of its output.
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        int issued = 0;
-        bool alive = true;
-        auto issue = [&]() {  // copies of slot `issued`, once the MMAs that read its previous contents are done
-            const int slot = issued % kTSlots;
-            if (!warp_wait(s32(&s_empty[slot]), ((issued / kTSlots) & 1) ^ 1, failed)) {
-                alive = false;
-                return;
-            }
-            const uint32_t b_tile = tiles + (slot >> 1) * kTStage + kTA;
-            const __half *src = xh + static_cast<size_t>(tok0) * cols + (issued >> 1) * kTK + (slot & 1) * 32;
+    } else if (warp == kLoadWarp) {
+        // ---- activation tiles: one thread, one TMA tile copy per accumulator column block and stage (64 columns x kBN rows,
+        //      written in the same 128-byte swizzle; no multicast; rows beyond ntok exist in the buffer and are zero).  A stage
+        //      is refilled once the MMAs of its second half are done (MMAs complete in order).
+        if (lane == 0) {
+            // The kernel is launched while the conversion of the activations may still run (programmatic stream
+            // serialization); this thread is the only reader of its output.
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int k = 0; k < n_k; ++k) {
+                const int stage = k % kTStages, use = k / kTStages;
+                if (!bar_wait(s32(&s_empty[2 * stage + 1]), (use & 1) ^ 1, failed)) break;
+                const uint32_t bar = s32(&s_xfull[stage]);
 #if VQM_TC5_ABLATE & 2
-            for (int i = b; i < 0; i += kBThreads) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 #else
-            for (int i = b; i < NH * kBN * 4; i += kBThreads) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(NH * kBN * 128) : "memory");
+#pragma unroll
+                for (int nh = 0; nh < NH; ++nh)
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                     tiles + stage * kTStage + kTA + nh * kBN * 128),
+                                 "l"(&x_map), "r"(k * kTK), "r"(tok0 + nh * kTNH + static_cast<int>(rank) * kBN), "r"(bar)
+                                 : "memory");
 #endif
-                const int n = i >> 2, c = (slot & 1) * 4 + (i & 3);  // (the decoder warps' row order was tried here: slower)
-                const int tok = (n / kBN) * kTNH + static_cast<int>(rank) * kBN + n % kBN;  // within the block's tile of tokens
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_tile + n * 128 + ((c ^ (n & 7)) << 4)),
-                             "l"(src + static_cast<size_t>(tok) * cols + (i & 3) * 8)
-                             : "memory");
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            ++issued;
-        };
-        constexpr int kWindow = kTSlots - 1;  // slots whose copies are in flight per thread
-        while (alive && issued < n_slots && issued < kWindow) issue();
-        for (int q = 0; alive && q < n_slots; ++q) {
-            // groups complete in order: slot q has landed once at most (issued - q - 1) groups are still pending
-            switch (issued - q - 1) {
-                case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-                case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-                case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-                case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-                case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-                case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-                default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            full_arrive(q % kTSlots);
-            if (issued < n_slots) issue();
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (lane == 0 && rank != 0) {
         // ---- second block of a pair: tell the first block about every slot that is full here
         for (int q = 0; q < n_slots; ++q) {
             const int slot = q % kTSlots;
             if (!bar_wait(s32(&s_full[slot]), (q / kTSlots) & 1, failed)) break;
+            if ((q & 1) == 0 && !bar_wait(s32(&s_xfull[slot >> 1]), (q / kTSlots) & 1, failed)) break;  // this block's activation tile too
             bar_arrive_cluster(in_block(s32(&s_full[slot]), 0));
         }
     } else if (lane == 0) {
@@ -665,6 +644,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
             const int slot = q % kTSlots;
 #if !(VQM_TC5_ABLATE & 8)
             if (!(PAIR ? bar_wait_cluster(s32(&s_full[slot]), (q / kTSlots) & 1, failed) : bar_wait(s32(&s_full[slot]), (q / kTSlots) & 1, failed))) break;
+            if ((q & 1) == 0 && !bar_wait(s32(&s_xfull[slot >> 1]), (q / kTSlots) & 1, failed)) break;  // the stage's activation tile
 #endif
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t a_desc = sw128_desc(tiles + (slot >> 1) * kTStage), b_desc = sw128_desc(tiles + (slot >> 1) * kTStage + kTA);
@@ -732,6 +712,9 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const uint8_t *
     }
 }
 
+using PFN_encodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
 template <int TYPE, int MR, int NH, bool PAIR>
 cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
                          unsigned *status, cudaStream_t stream) {
@@ -745,13 +728,34 @@ cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows,
         configured = true;
     }
     constexpr int kRowsPerUnit = kTM * MR * (PAIR ? 2 : 1);  // weight rows of a block, or of a pair of blocks
+    // The activations as a 2-D tensor [padded activation rows][cols] of fp16; a tile is 64 columns (one 128-byte swizzled
+    // row each) of the activation rows one block holds of an accumulator.
+    CUtensorMap x_map;
+    {
+        static PFN_encodeTiled encode = nullptr;
+        if (encode == nullptr) {
+            void *fn = nullptr;
+            cudaDriverEntryPointQueryResult found;
+            const cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found);
+            if (err != cudaSuccess) return err;
+            if (fn == nullptr || found != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+            encode = reinterpret_cast<PFN_encodeTiled>(fn);
+        }
+        const int tile = 2 * kTNH, padded = (ntok + tile - 1) / tile * tile;  // the runtime pads the buffer to gemm_tc5_token_tile()
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(padded)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+        const cuuint32_t box[2] = {kTK, PAIR ? kTNH / 2 : kTNH}, elem[2] = {1, 1};
+        if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(xh), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((rows + kRowsPerUnit - 1) / kRowsPerUnit * (PAIR ? 2 : 1), (ntok + kTNH * NH - 1) / (kTNH * NH));
     cfg.blockDim = dim3(kTThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     // May start while the kernel before it in the stream (the fp32 -> fp16 conversion of the activations) still runs: the
-    // set-up, the first weight copies and the first decoded tiles overlap it; the activation loaders wait for it.
+    // set-up, the first weight copies and the first decoded tiles overlap it; the thread that feeds the activations waits for it.
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -765,7 +769,7 @@ cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows,
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    return cudaLaunchKernelEx(&cfg, qgemm_tc5_kernel<TYPE, MR, NH, PAIR>, w, xh, y, rows, cols, row_bytes, ntok, codebook, status);
+    return cudaLaunchKernelEx(&cfg, qgemm_tc5_kernel<TYPE, MR, NH, PAIR>, x_map, w, y, rows, cols, row_bytes, ntok, codebook, status);
 }
 
 template <int TYPE>
