@@ -2,10 +2,10 @@
 //
 // Same contract as the warp-level kernel in vqm_gemm.cu (replaces the reference's vinf_qgemm_kernel,
 // engine/csrc/megakernel/qwen_runtime.cu:655-769: fp16 operands, fp32 accumulation), built on tcgen05:
-//   * a block owns 128 or 256 weight rows (one or two MMA M-halves) and 256 or 512 activation rows, as one or two
-//     accumulators of 128 x 256 fp32 in tensor memory (at most 512 columns, the whole TMEM of an SM: one block per SM);
-//     the shapes and when each is used are listed at stage_bytes below;
-//   * two blocks of a cluster can work as a pair (tcgen05.mma.cta_group::2, M = 256): each decodes its own 128 weight rows
+//   * a block owns 128 weight rows per MMA M-half and 256 activation rows per accumulator, as one or two accumulators of
+//     128 x 256 fp32 in tensor memory (at most 512 columns, the whole TMEM of an SM: one block per SM); the shapes are
+//     listed at stage_bytes below;
+//   * two blocks of a cluster work as a pair (tcgen05.mma.cta_group::2, M = 256): each decodes its own 128 weight rows
 //     per accumulator and holds half of the accumulator's 256 activation rows in its shared memory, which halves what a
 //     block reads of the activations from L2; the first block issues the MMAs for both and commits to the barriers of
 //     both (multicast commit), the second block forwards its "full" slots to the first with one remote arrive per slot,
@@ -14,22 +14,22 @@
 //     into a ring of two shared-memory buffers, one copy per row issued by the row's first decoder thread, so that the
 //     decoders never wait for global memory (types whose 256 columns are too wide for the ring - Q8_0, F16, F32 - are
 //     decoded straight from global memory);
-//   * K is walked in stages of 64, each filled and consumed as two halves of 32 (four pipeline slots in two stage
-//     buffers): warps 0-15 dequantise the weight half-tile (four threads per row, one chunk of 8 weights each and row
-//     half) with the exact block decoders - for Q4_K / Q5_K with a per-block header and constant shifts, see FastHeader -
-//     and store it as fp16 in the K-major 128-byte-swizzled layout the tensor core reads; warps 16-18 copy the fp16
-//     activation half-tile into the same layout with cp.async (the copies of three slots in flight per thread); both
-//     sides make their writes visible to the async proxy and arrive, once per warp, on the slot's "full" mbarrier;
-//   * one thread of warp 19 issues, per slot, 2 K-steps x the accumulators of tcgen05.mma (kind::f16, M = 128, N = 256,
-//     K = 16) from shared-memory descriptors and commits them to the slot's "empty" mbarrier, which hands the slot
-//     back to the producers, so tile production runs up to three slots ahead of the MMAs;
+//   * K is walked in stages of 64 (two to four stage buffers, as many as fit), each weight stage filled and consumed as
+//     two halves of 32 (the pipeline's slots): warps 0-15 dequantise the weight half-tile (four threads per row, one
+//     chunk of 8 weights each) with the exact block decoders - Q4_K, Q5_K, Q6_K and Q3_K with a per-block header and
+//     constant shifts, see FastHeader - store it as fp16 in the K-major 128-byte-swizzled layout the tensor core reads,
+//     make the writes visible to the async proxy and arrive, once per warp, on the slot's "full" mbarrier;
+//   * one thread of warp 16 feeds the activations: per stage one TMA tile copy (cp.async.bulk.tensor.2d, 64 columns x
+//     the block's activation rows of an accumulator, written by the hardware in the same 128-byte swizzle; no
+//     multicast) that completes on the stage's own mbarrier; a stage is refilled once the MMAs of its second half are done;
+//   * one thread of warp 17 issues, per slot, 2 K-steps x the accumulators of tcgen05.mma (kind::f16, N = 256, K = 16)
+//     from shared-memory descriptors and commits them to the slot's "empty" mbarrier, which hands the slot back to the
+//     producers, so tile production runs up to a ring's length ahead of the MMAs;
 //   * after the last commit, warps 0-15 read the accumulators with tcgen05.ld (warp w reads lanes 32 (w % 4) onwards, one
-//     weight row per thread and row half; the four warps of a lane group share the columns) and store y; a warp stores 32
+//     weight row per thread; the four warps of a lane group share the columns) and store y; a warp stores 32
 //     consecutive rows of one activation row, 128 bytes.
-// Where the time goes (Q4_K 17408 x 5120, 512 activation rows, 141 us with the activation conversion; experiment builds
-// with VQM_TC5_ABLATE): the MMA issue loop alone, never waiting, 81 us (640 MMAs of 128 x 256 x 16 at about 1.7 GHz are
-// 50 us; the rest is the conversion kernel, the prologue and the epilogue that nothing overlaps); with the barriers but
-// neither decode nor activation copies 103 us; without the activation copies 126 us; without the decode 135 us.
+// Where the time goes: profiles/prompt_gemm_tc5_Q4_K_17408x5120x512.md has the step-by-step history, the ablation builds
+// (VQM_TC5_ABLATE) and the ncu figures.
 // Every mbarrier wait is bounded: on expiry the block records a status code, everybody falls through to the end, and
 // the tensor memory is released before the block returns.
 #include <cuda.h>  // CUtensorMap and the driver entry point that encodes one (types only; nothing links against the driver)
@@ -39,6 +39,9 @@
 #include "vqm_kernels.h"
 #include "vqm_steps.cuh"
 
+#ifndef VQM_TC5_SHAPE
+#define VQM_TC5_SHAPE 0  // experiment builds: block shape for more than 256 activation rows, see launch_t
+#endif
 #ifndef VQM_TC5_ABLATE
 #define VQM_TC5_ABLATE 0  // experiment builds (wrong results): 1 = fast decoders store zeros, 2 = no activation copies,
                          // 4 = no proxy fence by the producers, 8 = only the MMA issue loop runs, without waiting
@@ -48,10 +51,10 @@ namespace vqm {
 namespace {
 
 // A block computes kTM * MR weight rows by kTNH * NH activation rows: MR x NH accumulators of 128 x 256 in tensor memory
-// (MR * NH <= 2: 512 columns).  Shapes in use: 1 x 1, 2 x 1 (256 weight rows per block halve what the blocks together pull
-// out of L2 for the activations - every block reads its activation tile once per weight tile, 713 MB for 17408 x 5120 x
-// 512 at 1 x 2 - at the price of decoding every weight once per 256 instead of 512 activation rows), 1 x 2; alone or as a
-// pair of blocks (see stage_bytes).  launch_t picks.
+// (MR * NH <= 2: 512 columns), alone or as a pair of blocks (see stage_bytes).  In use: 1 x 1 pairs up to 256 activation
+// rows, 1 x 2 pairs above; 2 x 1 (256 weight rows per block halve what the blocks together read of the activations from
+// L2, at the price of decoding every weight twice as often) and single blocks are kept for experiment builds, launch_t
+// has the measurements.
 constexpr int kTM = 128, kTNH = 256, kTK = 64;
 constexpr int kMaxStages = 4;  // stages of the tile ring: as many as fit into shared memory, see stages_for
 constexpr int kTA1 = kTM * kTK * 2, kTB1 = kTNH * kTK * 2;  // 16 KB per 128 weight rows, 32 KB per 256 activation rows
@@ -775,13 +778,18 @@ cudaError_t launch_shape(const uint8_t *w, const __half *xh, float *y, int rows,
 template <int TYPE>
 cudaError_t launch_t(const uint8_t *w, const __half *xh, float *y, int rows, int cols, long long row_bytes, int ntok, const uint8_t *codebook,
                      unsigned *status, cudaStream_t stream) {
-    // Which shape for which case was measured on 17408 x 5120 weights (times with the conversion of the activations):
-    //   up to 256 activation rows: a pair of blocks with one accumulator each (108 us; a single block 113);
-    //   more: 256 weight rows per block pay only with a fast decoder (Q3_K with the generic one: 187 us instead of 172);
-    //   alone where the raw ring for 256 rows fits beside two stages (Q4_K 122 us, Q3_K 126; as a pair 126 / 131), as a pair
-    //   where it only fits beside the pair's smaller stages (Q5_K 131 us; 1 x 2 alone 137); the other types as pairs of
-    //   1 x 2 blocks (Q6_K 132 us, Q8_0 144; alone 141 / 149).
+    // Which shape for which case was measured on 17408 x 5120 weights with 512 activation rows (times with the conversion
+    // of the activations; VQM_TC5_SHAPE selects the alternatives in an experiment build):
+    //   0  pairs of 1 x 2 blocks: 99-101 us for the four K-quants with a fast decoder, IQ4_XS 106, Q8_0 133 - the default
+    //   1  single 1 x 2 blocks: the same for the K-quants, IQ4_XS 123, Q8_0 137
+    //   2  2 x 1 (256 weight rows per block; pairs where the raw ring only fits beside a pair's smaller stages): 114-122;
+    //      every weight is decoded once per 256 instead of once per 512 activation rows, which costs more than the halved
+    //      activation traffic saves now that TMA feeds the activation tiles
+    // Up to 256 activation rows: a pair of 1 x 1 blocks (90 us).
     if (ntok <= kTNH) return launch_shape<TYPE, 1, 1, true>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+#if VQM_TC5_SHAPE == 1
+    return launch_shape<TYPE, 1, 2, false>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+#elif VQM_TC5_SHAPE == 2
     if constexpr (has_fast_chunk(TYPE) && fits_two_row_halves(TYPE, false)) {
         return launch_shape<TYPE, 2, 1, false>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
     } else if constexpr (has_fast_chunk(TYPE) && fits_two_row_halves(TYPE, true)) {
@@ -789,6 +797,9 @@ cudaError_t launch_t(const uint8_t *w, const __half *xh, float *y, int rows, int
     } else {
         return launch_shape<TYPE, 1, 2, true>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
     }
+#else
+    return launch_shape<TYPE, 1, 2, true>(w, xh, y, rows, cols, row_bytes, ntok, codebook, status, stream);
+#endif
 }
 
 }  // namespace
