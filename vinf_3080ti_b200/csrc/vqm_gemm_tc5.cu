@@ -12,12 +12,12 @@
 //     each block drains its own 128 lanes of tensor memory;
 //   * the raw weight bytes come in by bulk copies (1-D TMA, no multicast), 256 columns of the block's rows at a time
 //     into a ring of two shared-memory buffers, one copy per row issued by the row's first decoder thread, so that the
-//     decoders never wait for global memory (types whose 256 columns are too wide for the ring - Q8_0, F16, F32 - are
-//     decoded straight from global memory);
+//     decoders never wait for global memory (F16 and F32, whose 256 columns are too wide for the ring, are decoded
+//     straight from global memory);
 //   * K is walked in stages of 64 (two to four stage buffers, as many as fit), each weight stage filled and consumed as
 //     two halves of 32 (the pipeline's slots): warps 0-15 dequantise the weight half-tile (four threads per row, one
-//     chunk of 8 weights each) with the exact block decoders - Q4_K, Q5_K, Q6_K and Q3_K with a per-block header and
-//     constant shifts, see FastHeader - store it as fp16 in the K-major 128-byte-swizzled layout the tensor core reads,
+//     chunk of 8 weights each) with the exact block decoders - Q4_K, Q5_K, Q6_K, Q3_K and Q8_0 with a per-block header
+//     and constant shifts, see FastHeader - store it as fp16 in the K-major 128-byte-swizzled layout the tensor core reads,
 //     make the writes visible to the async proxy and arrive, once per warp, on the slot's "full" mbarrier;
 //   * one thread of warp 16 feeds the activations: per stage one TMA tile copy (cp.async.bulk.tensor.2d, 64 columns x
 //     the block's activation rows of an accumulator, written by the hardware in the same 128-byte swizzle; no
@@ -72,11 +72,20 @@ __host__ __device__ constexpr int raw_run_bytes(int type) { return kRawCols / ch
 // slot of one row: the run, up to 14 bytes in front (the copy starts at the 16-byte boundary below), the decoders' reads
 // of up to 8 bytes behind, rounded to 16
 __host__ __device__ constexpr int raw_slot_bytes(int type) { return (raw_run_bytes(type) + 14 + 8 + 15) / 16 * 16; }
-__host__ __device__ constexpr bool raw_staged(int type) { return raw_run_bytes(type) <= 210; }  // every type up to Q6_K; not Q8_0, F16, F32 (the ring would not fit)
-__host__ __device__ constexpr int raw_ring_bytes(int type, int mr) { return raw_staged(type) ? 2 * mr * kTM * raw_slot_bytes(type) : 0; }
 __host__ __device__ constexpr int table_bytes16(int type) { return grid_bytes(type) > 0 ? (grid_bytes(type) + 15) / 16 * 16 : 16; }
+// Staged where the ring fits beside two stages of tiles: every quantised type in the shapes in use (Q8_0 only beside a
+// pair's smaller stages); F16 and F32 never.
+__host__ __device__ constexpr size_t smem_without_ring(int type, int mr, int nh, bool pair, int stages) {
+    return table_bytes16(type) + 1024 + static_cast<size_t>(stages) * stage_bytes(mr, nh, pair);
+}
+__host__ __device__ constexpr bool raw_staged(int type, int mr, int nh, bool pair) {
+    return raw_run_bytes(type) <= 272 && smem_without_ring(type, mr, nh, pair, 2) + 2 * mr * kTM * raw_slot_bytes(type) <= 227 * 1024;
+}
+__host__ __device__ constexpr int raw_ring_bytes(int type, int mr, int nh, bool pair) {
+    return raw_staged(type, mr, nh, pair) ? 2 * mr * kTM * raw_slot_bytes(type) : 0;
+}
 __host__ __device__ constexpr size_t tc5_smem_bytes(int type, int mr, int nh, bool pair, int stages) {
-    return table_bytes16(type) + 1024 + static_cast<size_t>(stages) * stage_bytes(mr, nh, pair) + raw_ring_bytes(type, mr);
+    return smem_without_ring(type, mr, nh, pair, stages) + raw_ring_bytes(type, mr, nh, pair);
 }
 // The ring is what hides the refill round trip of a slot (MMAs done -> "empty" -> copies from L2 / decode -> "full"),
 // which is several times longer than a slot's MMAs: every stage that fits is used.
@@ -86,7 +95,7 @@ __host__ __device__ constexpr int stages_for(int type, int mr, int nh, bool pair
     return s;
 }
 // 256 weight rows per block need the raw ring for 256 rows (reading them from global memory per chunk is too slow there)
-__host__ __device__ constexpr bool fits_two_row_halves(int type, bool pair) { return raw_staged(type) && tc5_smem_bytes(type, 2, 1, pair, 2) <= 227 * 1024; }
+[[maybe_unused]] __host__ __device__ constexpr bool fits_two_row_halves(int type, bool pair) { return raw_staged(type, 2, 1, pair); }
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -185,7 +194,7 @@ template <int N>
 struct Int {
     static constexpr int value = N;
 };
-__host__ __device__ constexpr bool has_fast_chunk(int type) { return type == kQ4_K || type == kQ5_K || type == kQ6_K || type == kQ3_K; }
+__host__ __device__ constexpr bool has_fast_chunk(int type) { return type == kQ4_K || type == kQ5_K || type == kQ6_K || type == kQ3_K || type == kQ8_0; }
 
 __device__ __forceinline__ uint32_t f16x2_of(f32x2 v) {  // (lo, hi) -> two fp16 in one word, round to nearest even
     float lo, hi;
@@ -333,6 +342,23 @@ struct FastHeader<kQ3_K> {
     }
 };
 
+// Q8_0 (engine/csrc/common/qwen_quant.cuh:163-170): blocks of 32 weights, d @0 and 32 int8 @2; slot G of a 256-column run is
+// its block G, the thread's chunk the 8 bytes at 2 + 8 * quarter of it.  Nothing to unpack per run.
+template <>
+struct FastHeader<kQ8_0> {
+    __device__ __forceinline__ void load(uint32_t, int) {}
+    template <int G>
+    __device__ __forceinline__ void chunk(uint32_t blk, int quarter, uint32_t (&h)[4]) const {
+        const uint32_t at = blk + G * 34;
+        const float d = half_bits_to_float(lds16(at));
+        uint32_t w0, w1;
+        lds64_a2(at + 2 + 8 * quarter, w0, w1);
+        const f32x2 neg_magic = pack2(-(8388608.0f + 128.0f), -(8388608.0f + 128.0f)), d2 = pack2(d, d);
+        bytes_mul_f16(w0 ^ 0x80808080u, neg_magic, d2, h[0], h[1]);  // int8 + 128 is the unsigned byte
+        bytes_mul_f16(w1 ^ 0x80808080u, neg_magic, d2, h[2], h[3]);
+    }
+};
+
 // (types without a fast decoder never instantiate this)
 template <int TYPE>
 struct FastHeader {
@@ -396,7 +422,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const __grid_co
     // table first, then the stages on a 1024-byte boundary (the swizzle works on absolute shared-memory address bits)
     uint8_t *table = tc5_raw;
     const uint32_t tiles = (s32(tc5_raw) + TABLE + 1023u) & ~1023u;
-    constexpr bool kStaged = raw_staged(TYPE);
+    constexpr bool kStaged = raw_staged(TYPE, MR, NH, PAIR);
     constexpr int RSLOT = raw_slot_bytes(TYPE), RUN = raw_run_bytes(TYPE);
     const uint32_t raw_ring = tiles + kTStages * kTStage;  // two buffers of MR * kTM row slots
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
