@@ -353,9 +353,9 @@ def prefill_gemm(rt, torch, stream, dev, peaks: dict) -> dict:
     return {"tensor": f"{t.name} {rows}x{cols}", "activation_rows": ntok, "ms": round(ms, 4), "ms_median": round(statistics.median(times), 4),
             "TFLOPs": round(flops / ms / 1e9, 1), "frac_of_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4),
             "frac_of_bf16_sustained": round(flops / ms / 1e9 / peaks["bf16_tflops_sustained"], 4) if peaks.get("bf16_tflops_sustained") else None,
-            "note": "fp32 activations -> fp16, weights dequantised to fp16 tiles (raw blocks staged in shared memory, per-block decoders), "
-                    "tcgen05 MMA with fp32 accumulators in tensor memory, 256 weight rows x 256 activation rows per block (other types and "
-                    "smaller passes: pairs of blocks on cta_group::2); "
+            "note": "fp32 activations -> fp16; pairs of blocks on tcgen05.mma.cta_group::2, each 128 weight rows x 512 activation rows with fp32 "
+                    "accumulators in tensor memory; weights: raw blocks staged in shared memory by bulk copies, per-block decoders to fp16 "
+                    "tiles; activations: TMA tile copies; "
                     "time includes the fp32 -> fp16 conversion of the activations"}
 
 
