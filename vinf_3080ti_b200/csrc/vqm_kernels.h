@@ -89,8 +89,9 @@ cudaError_t launch_f32_to_f16_rows(const float *x, void *xh, long long n_valid, 
 cudaError_t launch_qgemm(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
                          const uint8_t *codebook, cudaStream_t stream);
 
-// Prompt-pass GEMM on tcgen05 tensor cores with the accumulators in tensor memory (vqm_gemm_tc5.cu): 512 activation rows
-// per block; needs cols to be a multiple of 64.  status: device word that receives a code if a bounded wait expires.
+// Prompt-pass GEMM on tcgen05 tensor cores with the accumulators in tensor memory (vqm_gemm_tc5.cu): xh padded to
+// gemm_tc5_token_tile() rows; needs cols to be a multiple of 64.  status: device word that receives a code if a bounded
+// wait expires.
 int gemm_tc5_token_tile();
 bool gemm_tc5_supports(int cols);
 cudaError_t launch_qgemm_tc5(int type, const uint8_t *w, const void *xh, float *y, int rows, int cols, long long row_bytes, int ntok,
