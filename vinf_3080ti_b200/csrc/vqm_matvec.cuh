@@ -646,9 +646,11 @@ __global__ void __launch_bounds__(kWarps * 32, VQM_MIN_BLOCKS(M, RW)) qmv_kernel
         }
         // Release at GPU scope: this block's stores (remote ones included) happen before its count below; the last
         // block's system-scope fence is cumulative over everything it has observed through the counter.
-        __threadfence();
         __syncthreads();
-        if (threadIdx.x == 0) s_last = atomicAdd(a.done_counter, 1u) == gridDim.x - 1;
+        if (threadIdx.x == 0) {
+            __threadfence();  // after the barrier, cumulative over the stores of the whole block
+            s_last = atomicAdd(a.done_counter, 1u) == gridDim.x - 1;
+        }
         __syncthreads();
         if (s_last) {
             if (want_push) __threadfence_system();
