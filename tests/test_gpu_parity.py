@@ -503,6 +503,27 @@ def test_prompt_gemm_tcgen05_matches_the_matvec_path_for_every_type(rt, codebook
     assert rel_l2(got, oracle) <= 2e-3  # fp16 rounding of both operands
 
 
+@pytest.mark.parametrize("ntok", [130, 300])
+@pytest.mark.parametrize("t", [T.Q8_0, T.IQ4_NL, T.F16, T.F32], ids=lambda t: t.name)
+def test_prompt_gemm_tcgen05_columns_that_end_inside_a_run_of_256(rt, codebooks, t, ntok):
+    """Types with blocks of 32 weights (or none) allow column counts that are not multiples of 256: the kernel's last run of
+    raw blocks is then short (320 columns: one full run and a quarter of one)."""
+    rng = np.random.default_rng(7300 + int(t) + ntok)
+    rows, cols = 150, 320
+    raw = synthetic_blocks(t, rows, cols, rng)
+    x = synthetic_activations(ntok, cols, rng)
+    ref = run_qmv(rt, raw, t, rows, cols, x)
+    rt.set_gemm_min_rows(64)
+    try:
+        rt.zero("y")
+        rt.qmv("w", "x", "y", ntok)
+        rt.synchronize()
+        got = rt.read_array("y").reshape(ntok, rows)
+    finally:
+        rt.set_gemm_min_rows(0)
+    assert np.all(np.abs(got - ref) <= 3e-3 * np.abs(ref).max())
+
+
 @pytest.mark.parametrize("ntok", [256, 512])
 @pytest.mark.parametrize("t", ALL_TYPES, ids=lambda t: t.name)
 def test_prompt_gemm_tiles_hold_the_dequantised_weights_rounded_to_fp16(rt, codebooks, t, ntok):

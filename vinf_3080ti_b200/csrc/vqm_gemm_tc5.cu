@@ -589,6 +589,7 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const __grid_co
                     for (int mr = 0; mr < MR; ++mr) hdr[mr].load(blk[mr], quarter);
                     auto one = [&](auto g_tag) -> bool {
                         constexpr int G = decltype(g_tag)::value;
+                        if (col * kSlotsPerCol + G >= n_slots) return true;  // the last run of a 32-weight-block type may be short
                         if (!slot_begin(col, G)) return false;
 #pragma unroll
                         for (int mr = 0; mr < MR; ++mr) {
