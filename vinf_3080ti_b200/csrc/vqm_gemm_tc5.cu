@@ -253,13 +253,6 @@ template <>
 struct FastHeader<kQ4_K> : FastHeaderK45<kQ4_K> {};
 template <>
 struct FastHeader<kQ5_K> : FastHeaderK45<kQ5_K> {};
-// Eight bytes at a 2-byte aligned shared address: three aligned words and two funnel shifts.
-__device__ __forceinline__ void lds64_a2(uint32_t a, uint32_t &lo, uint32_t &hi) {
-    const uint32_t b = a & ~3u, sh = (a & 2u) * 8u;
-    const uint32_t w0 = lds32(b), w1 = lds32(b + 4), w2 = lds32(b + 8);
-    lo = __funnelshift_r(w0, w1, sh);
-    hi = __funnelshift_r(w1, w2, sh);
-}
 // the four bytes of `w` (minus the bias inside neg_magic) times dl (packed), as fp16
 __device__ __forceinline__ void bytes_mul_f16(uint32_t w, f32x2 neg_magic, f32x2 dl, uint32_t &h0, uint32_t &h1) {
     h0 = f16x2_of(mul2(bytes_to_pair<0, 1>(w, neg_magic), dl));

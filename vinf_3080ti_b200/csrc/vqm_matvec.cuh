@@ -41,6 +41,7 @@
 #include "vqm_steps_kquants.cuh"
 #include "vqm_steps_iq4.cuh"
 #include "vqm_steps_grid.cuh"
+#include "vqm_steps_plain.cuh"
 
 namespace vqm {
 

@@ -61,6 +61,14 @@ __device__ __forceinline__ uint32_t lds32_a2(uint32_t a) {
     return __funnelshift_r(lds32(b), lds32(b + 4), (a & 2u) * 8u);
 }
 
+// Eight bytes at a 2-byte aligned shared address: three aligned words and two funnel shifts.
+__device__ __forceinline__ void lds64_a2(uint32_t a, uint32_t &lo, uint32_t &hi) {
+    const uint32_t b = a & ~3u, sh = (a & 2u) * 8u;
+    const uint32_t w0 = lds32(b), w1 = lds32(b + 4), w2 = lds32(b + 8);
+    lo = __funnelshift_r(w0, w1, sh);
+    hi = __funnelshift_r(w1, w2, sh);
+}
+
 // ---- packed fp32 arithmetic ------------------------------------------------------------------------------
 
 // Two fp32 values in one 64-bit register pair; sm_100 executes add/mul/fma on both halves with one
