@@ -53,24 +53,28 @@ template <int TYPE, int M, int RW>
 struct PlainStep {
     static constexpr int kScratch = 0;
     static constexpr float kOutScale = kSubOutScale;
-    static __device__ __forceinline__ void run(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t, uint32_t, uint32_t xs, int cols, int nrows,
-                                               f32x2 (&acc)[RW][M], int lane) {
-        constexpr int SLOT = slot_bytes(TYPE);
+    // NR rows, all decoded (a chunk's missing rows are computed from whatever their slots hold and dropped by the caller)
+    template <int NR>
+    struct Pass {
+        static __device__ __forceinline__ void go(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t xs, int cols, f32x2 (&acc)[RW][M], int lane) {
+            constexpr int SLOT = slot_bytes(TYPE);
+            uint32_t row[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) row[r] = stage + r * SLOT + ((d0 + r * rb16) & 15u);
 #pragma unroll 1
-        for (int j = 0; j < kChunksPerLane; ++j) {
-            const int chunk = j * 32 + lane;
-            if (chunk * 8 < cols) {
-                X4 xa[M], xb[M];
+            for (int j = 0; j < kChunksPerLane; ++j) {
+                const int chunk = j * 32 + lane;
+                if (chunk * 8 < cols) {
+                    X4 xa[M], xb[M];
 #pragma unroll
-                for (int t = 0; t < M; ++t) {
-                    xa[t] = lds_x4(xs + (t * kSegCols + chunk * 8) * 4);
-                    xb[t] = lds_x4(xs + (t * kSegCols + chunk * 8 + 4) * 4);
-                }
+                    for (int t = 0; t < M; ++t) {
+                        xa[t] = lds_x4(xs + (t * kSegCols + chunk * 8) * 4);
+                        xb[t] = lds_x4(xs + (t * kSegCols + chunk * 8 + 4) * 4);
+                    }
 #pragma unroll
-                for (int r = 0; r < RW; ++r) {
-                    if (r < nrows) {
+                    for (int r = 0; r < NR; ++r) {
                         f32x2 w[4];
-                        plain_chunk<TYPE>(stage + r * SLOT + ((d0 + r * rb16) & 15u), chunk, w);
+                        plain_chunk<TYPE>(row[r], chunk, w);
 #pragma unroll
                         for (int t = 0; t < M; ++t)
                             acc[r][t] = fma2(w[3], xb[t].p23, fma2(w[2], xb[t].p01, fma2(w[1], xa[t].p23, fma2(w[0], xa[t].p01, acc[r][t]))));
@@ -78,6 +82,10 @@ struct PlainStep {
                 }
             }
         }
+    };
+    static __device__ __forceinline__ void run(uint32_t stage, uint32_t d0, uint32_t rb16, uint32_t, uint32_t, uint32_t xs, int cols, int nrows,
+                                               f32x2 (&acc)[RW][M], int lane) {
+        dispatch_rows<Pass, RW>(nrows, stage, d0, rb16, xs, cols, acc, lane);
     }
 };
 
