@@ -7,7 +7,8 @@ The driver below issues, for a small synthetic model, the call sequence of the r
 MLP and LM head (qwen_gpu.py:862-883, 916-922, 1068-1086: rmsnorm, qmv q/k/v, split_gated_q, q/k norms, rope, kv_append,
 attention, sigmoid_mul, qmv o, add; rmsnorm, qmv gate/up, silu_mul, qmv down, add; rmsnorm, qmv output, argmax).  Greedy
 decoding for 20 steps and a 4-token verification pass must give the same token ids whether every call runs on the
-reference runtime or the matvecs run here."""
+reference runtime or the matvecs run here - as plain `qmv` calls, or through `qmv_fused`, which also takes over the
+rmsnorm, silu_mul, add and argmax launches around them."""
 from __future__ import annotations
 
 import numpy as np
@@ -36,8 +37,7 @@ class ProxyRuntime:
 
     def upload(self, name, data, type_, cols, rows):
         self.ref.upload(name, data, type_, cols, rows)
-        if type_ != int(T.F32) or rows > 1:  # norm weights (F32 vectors) are only read by the reference's kernels
-            self.mine.upload(name, data, type_, cols, rows)
+        self.mine.upload(name, data, type_, cols, rows)  # (the F32 norm vectors too: the fused matvecs read them)
 
     def _adopt(self, name):
         ptr, n = self.ref.buffer_ptr(name)
@@ -52,6 +52,16 @@ class ProxyRuntime:
         self.mine.qmv(weight, x, y, ntok)
         self.mine.synchronize()
         self.matvecs_here += 1
+
+    def qmv_fused(self, weight, x, y, ntok=1, **kw):
+        for name in (x, y, kw.get("silu_mul")):
+            if name is not None:
+                self._adopt(name)
+        self.ref.synchronize()
+        ids = self.mine.qmv_fused(weight, x, y, ntok, eps=EPS, **kw)
+        self.mine.synchronize()
+        self.matvecs_here += 1
+        return ids
 
 
 def build_model(seed: int):
@@ -148,6 +158,41 @@ class Driver:
         return np.frombuffer(self.rt.read("logits", n * VOCAB), dtype=np.float32).reshape(n, VOCAB).copy()
 
 
+class FusedDriver(Driver):
+    """The same model with this library's fused matvecs in place of rmsnorm -> qmv, silu_mul -> qmv -> add and
+    rmsnorm -> qmv -> argmax: five element-wise launches fewer per layer, two fewer for the LM head."""
+
+    def forward(self, tokens):
+        rt, n, pos = self.rt, len(tokens), self.position
+        rt.write("h", np.ascontiguousarray(self.embeddings[tokens]).tobytes())
+        for i in range(LAYERS):
+            p, kc, vc = f"blk.{i}.", f"kc.{i}", f"vc.{i}"
+            rt.qmv_fused(p + "attn_q.weight", "h", "q_raw", n, norm=p + "attn_norm.weight")
+            rt.qmv_fused(p + "attn_k.weight", "h", "k", n, norm=p + "attn_norm.weight")
+            rt.qmv_fused(p + "attn_v.weight", "h", "v", n, norm=p + "attn_norm.weight")
+            rt.split_gated_q("q_raw", "q", "q_gate", HEADS * n, HEAD_DIM)
+            rt.rmsnorm("q", p + "attn_q_norm.weight", "q", HEAD_DIM, EPS, HEADS * n)
+            rt.rmsnorm("k", p + "attn_k_norm.weight", "k", HEAD_DIM, EPS, KV_HEADS * n)
+            rt.rope("q", HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
+            rt.rope("k", KV_HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
+            rt.kv_append("k", "v", kc, vc, KV_HEADS, MAX_CTX, HEAD_DIM, pos, n)
+            rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, MAX_CTX, pos + 1, n)
+            rt.sigmoid_mul("attn", "q_gate", "attn", HEADS * HEAD_DIM * n)
+            rt.qmv_fused(p + "attn_output.weight", "attn", "h", n, add=True)
+            rt.qmv_fused(p + "ffn_gate.weight", "h", "mlp_gate", n, norm=p + "post_attention_norm.weight")
+            rt.qmv_fused(p + "ffn_up.weight", "h", "mlp_up", n, norm=p + "post_attention_norm.weight")
+            rt.qmv_fused(p + "ffn_down.weight", "mlp_gate", "h", n, silu_mul="mlp_up", add=True)
+        self.position += n
+        self.last = n
+
+    def greedy_next(self):
+        self.rt.copy("h_last", 0, "h", (self.last - 1) * HIDDEN, HIDDEN)
+        return self.rt.qmv_fused("output.weight", "h_last", "logits", 1, norm="output_norm.weight", argmax=True)[0]
+
+    def greedy_rows(self):
+        return self.rt.qmv_fused("output.weight", "h", "logits", self.last, norm="output_norm.weight", argmax=True)
+
+
 def decode(driver, prompt, steps):
     """Greedy decoding, then one 4-token verification pass; returns the ids and the smallest top-2 logit gap seen."""
     driver.forward(prompt)
@@ -190,5 +235,14 @@ def test_greedy_tokens_are_the_same_with_the_matvecs_routed_to_this_library(code
             mine.close()
         assert got_ids == want_ids
         assert got_rows == want_rows
+        mine = Runtime(codebooks["iq3s_grid"], codebooks)
+        try:
+            proxy = ProxyRuntime(mod.Runtime(codebooks["iq3s_grid"]), mine)
+            fused_ids, fused_rows, _ = decode(FusedDriver(proxy, tensors, embeddings), prompt, 20)
+            assert proxy.matvecs_here == 22 * 7 * LAYERS + 21
+        finally:
+            mine.close()
+        assert fused_ids == want_ids
+        assert fused_rows == want_rows
         return
     pytest.fail("every synthetic model had a near tie in its reference logits or repeated itself")
