@@ -96,21 +96,20 @@ def build_model(seed: int):
 class Driver:
     """The reference executor's call order for full-attention layers, on whatever runtime it is given."""
 
-    ROWS = 8  # activation rows a pass may have
-    BUFFERS = {"h": ROWS * HIDDEN, "xn": ROWS * HIDDEN, "q_raw": ROWS * 2 * HEADS * HEAD_DIM, "q": ROWS * HEADS * HEAD_DIM,
-               "q_gate": ROWS * HEADS * HEAD_DIM, "k": ROWS * KV_HEADS * HEAD_DIM, "v": ROWS * KV_HEADS * HEAD_DIM,
-               "attn": ROWS * HEADS * HEAD_DIM, "proj": ROWS * HIDDEN, "mlp_gate": ROWS * INTER, "mlp_up": ROWS * INTER,
-               "h_last": HIDDEN, "logits": ROWS * VOCAB}
-
-    def __init__(self, rt, tensors, embeddings):
-        self.rt, self.embeddings, self.position = rt, embeddings, 0
-        for name, (data, type_, cols, rows) in tensors.items():
-            rt.upload(name, data, type_, cols, rows)
-        for name, n in self.BUFFERS.items():
+    def __init__(self, rt, tensors, embeddings, rows=8, max_ctx=MAX_CTX):
+        """rows: activation rows a pass may have (logits are kept for 8 of them)."""
+        self.rt, self.embeddings, self.position, self.max_ctx = rt, embeddings, 0, max_ctx
+        for name, (data, type_, cols, nrows) in tensors.items():
+            rt.upload(name, data, type_, cols, nrows)
+        buffers = {"h": rows * HIDDEN, "xn": rows * HIDDEN, "q_raw": rows * 2 * HEADS * HEAD_DIM, "q": rows * HEADS * HEAD_DIM,
+                   "q_gate": rows * HEADS * HEAD_DIM, "k": rows * KV_HEADS * HEAD_DIM, "v": rows * KV_HEADS * HEAD_DIM,
+                   "attn": rows * HEADS * HEAD_DIM, "proj": rows * HIDDEN, "mlp_gate": rows * INTER, "mlp_up": rows * INTER,
+                   "h_last": HIDDEN, "logits": 8 * VOCAB}
+        for name, n in buffers.items():
             rt.alloc(name, n)
         for i in range(LAYERS):
-            rt.alloc(f"kc.{i}", KV_HEADS * HEAD_DIM * MAX_CTX)
-            rt.alloc(f"vc.{i}", KV_HEADS * HEAD_DIM * MAX_CTX)
+            rt.alloc(f"kc.{i}", KV_HEADS * HEAD_DIM * max_ctx)
+            rt.alloc(f"vc.{i}", KV_HEADS * HEAD_DIM * max_ctx)
 
     def forward(self, tokens):
         rt, n, pos = self.rt, len(tokens), self.position
@@ -126,8 +125,8 @@ class Driver:
             rt.rmsnorm("k", p + "attn_k_norm.weight", "k", HEAD_DIM, EPS, KV_HEADS * n)
             rt.rope("q", HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
             rt.rope("k", KV_HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
-            rt.kv_append("k", "v", kc, vc, KV_HEADS, MAX_CTX, HEAD_DIM, pos, n)
-            rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, MAX_CTX, pos + 1, n)
+            rt.kv_append("k", "v", kc, vc, KV_HEADS, self.max_ctx, HEAD_DIM, pos, n)
+            rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, self.max_ctx, pos + 1, n)
             rt.sigmoid_mul("attn", "q_gate", "attn", HEADS * HEAD_DIM * n)
             rt.qmv(p + "attn_output.weight", "attn", "proj", n)
             rt.add("h", "proj", "h", HIDDEN * n)
@@ -175,8 +174,8 @@ class FusedDriver(Driver):
             rt.rmsnorm("k", p + "attn_k_norm.weight", "k", HEAD_DIM, EPS, KV_HEADS * n)
             rt.rope("q", HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
             rt.rope("k", KV_HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
-            rt.kv_append("k", "v", kc, vc, KV_HEADS, MAX_CTX, HEAD_DIM, pos, n)
-            rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, MAX_CTX, pos + 1, n)
+            rt.kv_append("k", "v", kc, vc, KV_HEADS, self.max_ctx, HEAD_DIM, pos, n)
+            rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, self.max_ctx, pos + 1, n)
             rt.sigmoid_mul("attn", "q_gate", "attn", HEADS * HEAD_DIM * n)
             rt.qmv_fused(p + "attn_output.weight", "attn", "h", n, add=True)
             rt.qmv_fused(p + "ffn_gate.weight", "h", "mlp_gate", n, norm=p + "post_attention_norm.weight")
@@ -246,3 +245,54 @@ def test_greedy_tokens_are_the_same_with_the_matvecs_routed_to_this_library(code
         assert fused_rows == want_rows
         return
     pytest.fail("every synthetic model had a near tie in its reference logits or repeated itself")
+
+
+def test_a_prompt_pass_through_the_tensor_core_gemm_under_the_reference_runtime(codebooks):
+    """Prompt mode: 192 prompt rows in one pass with set_gemm_min_rows(64) on both sides - the reference's own tensor-core
+    GEMM there, the tcgen05 GEMM here (fp16 operands in both, so the hidden states agree to fp16 rounding, not bit for
+    bit) - followed by greedy decoding through the matvec path.  The hidden rows after the prompt must agree within 1e-2
+    relative L2, and the decoded tokens must be equal when the reference's own logits are not near a tie."""
+    mod = oracle_libs.load_reference_cuda_module()
+    if mod is None:
+        pytest.skip("oracle/_ref/_cuda_qwen_runtime.so has not been built (make -C oracle ref REFERENCE=...)")
+    from vinf_3080ti_b200.runtime import Runtime
+
+    n_prompt, steps = 192, 8
+    for seed in (21, 22, 23, 24):
+        tensors, embeddings = build_model(seed)
+        prompt = [int(v) for v in np.random.default_rng(seed).integers(0, VOCAB, size=n_prompt)]
+        ref_rt = mod.Runtime(codebooks["iq3s_grid"])
+        ref_rt.set_gemm_min_rows(64)
+        reference = Driver(ref_rt, tensors, embeddings, rows=n_prompt, max_ctx=256)
+        reference.forward(prompt)
+        ref_rt.synchronize()
+        want_h = np.frombuffer(ref_rt.read("h", n_prompt * HIDDEN), dtype=np.float32).reshape(n_prompt, HIDDEN).copy()
+        want_ids, gap = [], np.inf
+        for _ in range(steps):
+            nxt = reference.greedy_next()
+            top = np.sort(reference.logits(1)[0])[-2:]
+            gap = min(gap, float(top[1] - top[0]))
+            want_ids.append(int(nxt))
+            reference.forward([nxt])
+        if gap < 0.01 * float(np.abs(reference.logits(1)).max()):  # fp16 operands move logits by ~1e-3 of their size
+            continue
+        mine = Runtime(codebooks["iq3s_grid"], codebooks)
+        try:
+            mine.set_gemm_min_rows(64)
+            proxy_ref = mod.Runtime(codebooks["iq3s_grid"])
+            proxy = ProxyRuntime(proxy_ref, mine)
+            driver = Driver(proxy, tensors, embeddings, rows=n_prompt, max_ctx=256)
+            driver.forward(prompt)
+            proxy_ref.synchronize()
+            got_h = np.frombuffer(proxy_ref.read("h", n_prompt * HIDDEN), dtype=np.float32).reshape(n_prompt, HIDDEN).copy()
+            got_ids = []
+            for _ in range(steps):
+                nxt = driver.greedy_next()
+                got_ids.append(int(nxt))
+                driver.forward([nxt])
+        finally:
+            mine.close()
+        assert np.linalg.norm(got_h - want_h) / np.linalg.norm(want_h) <= 1e-2
+        assert got_ids == want_ids
+        return
+    pytest.fail("every synthetic model had a near tie in its reference logits")
