@@ -5,7 +5,9 @@ to this library on the SAME device buffers (found with the reference's buffer_pt
 
 The driver below issues, for a small synthetic model, the call sequence of the reference executor's full-attention layer,
 MLP and LM head (qwen_gpu.py:862-883, 916-922, 1068-1086: rmsnorm, qmv q/k/v, split_gated_q, q/k norms, rope, kv_append,
-attention, sigmoid_mul, qmv o, add; rmsnorm, qmv gate/up, silu_mul, qmv down, add; rmsnorm, qmv output, argmax).  Greedy
+attention, sigmoid_mul, qmv o, add; rmsnorm, qmv gate/up, silu_mul, qmv down, add; rmsnorm, qmv output, argmax) and of
+its linear-attention layer (:885-914: rmsnorm, qmv qkv / gate / beta / alpha, conv_update, gated_delta, gated_rmsnorm,
+qmv out, add).  Greedy
 decoding for 20 steps and a 4-token verification pass must give the same token ids whether every call runs on the
 reference runtime or the matvecs run here - as plain `qmv` calls, or through `qmv_fused`, which also takes over the
 rmsnorm, silu_mul, add and argmax launches around them."""
@@ -22,6 +24,11 @@ pytestmark = pytest.mark.gpu
 
 HIDDEN, HEADS, KV_HEADS, HEAD_DIM, ROTARY, INTER, VOCAB, LAYERS, MAX_CTX = 512, 8, 2, 64, 32, 1024, 2048, 3, 64
 EPS, FREQ_BASE = 1e-6, 10000.0
+# linear-attention (gated delta rule) layers: key heads, value heads, their dimensions, causal-convolution width
+KEY_HEADS, VALUE_HEADS, KEY_DIM, VALUE_DIM, CONV_K = 2, 4, 64, 64, 4
+CONV_DIM, VALUE_ALL = 2 * KEY_HEADS * KEY_DIM + VALUE_HEADS * VALUE_DIM, VALUE_HEADS * VALUE_DIM
+LINEAR_LAYERS = (0, 2)  # the layer schedule: linear, full attention, linear
+MATVECS_PER_PASS = sum(8 if i in LINEAR_LAYERS else 7 for i in range(LAYERS))
 
 
 class ProxyRuntime:
@@ -74,15 +81,29 @@ def build_model(seed: int):
     def norm(name, n):
         tensors[name] = ((1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32).tobytes(), int(T.F32), n, 1)
 
+    def vector(name, values):
+        tensors[name] = (np.ascontiguousarray(values, dtype=np.float32).tobytes(), int(T.F32), len(values), 1)
+
     for i in range(LAYERS):
         p = f"blk.{i}."
         norm(p + "attn_norm.weight", HIDDEN)
-        quant(p + "attn_q.weight", T.Q6_K, 2 * HEADS * HEAD_DIM, HIDDEN)  # query and its gate, interleaved per head
-        quant(p + "attn_k.weight", T.Q6_K, KV_HEADS * HEAD_DIM, HIDDEN)
-        quant(p + "attn_v.weight", T.Q8_0, KV_HEADS * HEAD_DIM, HIDDEN)
-        norm(p + "attn_q_norm.weight", HEAD_DIM)
-        norm(p + "attn_k_norm.weight", HEAD_DIM)
-        quant(p + "attn_output.weight", T.Q5_K, HIDDEN, HEADS * HEAD_DIM)
+        if i in LINEAR_LAYERS:
+            quant(p + "attn_qkv.weight", T.Q5_K, CONV_DIM, HIDDEN)
+            quant(p + "attn_gate.weight", T.Q4_K, VALUE_ALL, HIDDEN)
+            quant(p + "ssm_beta.weight", T.Q8_0, VALUE_HEADS, HIDDEN)  # a handful of rows, as in the real model
+            quant(p + "ssm_alpha.weight", T.F32, VALUE_HEADS, HIDDEN)
+            vector(p + "ssm_conv1d.weight", 0.3 * rng.standard_normal(CONV_DIM * CONV_K))
+            vector(p + "ssm_a", -np.exp(rng.uniform(-1.0, 1.0, VALUE_HEADS)))
+            vector(p + "ssm_dt.bias", rng.uniform(-1.0, 1.0, VALUE_HEADS))
+            norm(p + "ssm_norm.weight", VALUE_DIM)
+            quant(p + "ssm_out.weight", T.Q6_K, HIDDEN, VALUE_ALL)
+        else:
+            quant(p + "attn_q.weight", T.Q6_K, 2 * HEADS * HEAD_DIM, HIDDEN)  # query and its gate, interleaved per head
+            quant(p + "attn_k.weight", T.Q6_K, KV_HEADS * HEAD_DIM, HIDDEN)
+            quant(p + "attn_v.weight", T.Q8_0, KV_HEADS * HEAD_DIM, HIDDEN)
+            norm(p + "attn_q_norm.weight", HEAD_DIM)
+            norm(p + "attn_k_norm.weight", HEAD_DIM)
+            quant(p + "attn_output.weight", T.Q5_K, HIDDEN, HEADS * HEAD_DIM)
         norm(p + "post_attention_norm.weight", HIDDEN)
         quant(p + "ffn_gate.weight", T.Q3_K, INTER, HIDDEN)
         quant(p + "ffn_up.weight", T.IQ4_XS, INTER, HIDDEN)
@@ -104,12 +125,26 @@ class Driver:
         buffers = {"h": rows * HIDDEN, "xn": rows * HIDDEN, "q_raw": rows * 2 * HEADS * HEAD_DIM, "q": rows * HEADS * HEAD_DIM,
                    "q_gate": rows * HEADS * HEAD_DIM, "k": rows * KV_HEADS * HEAD_DIM, "v": rows * KV_HEADS * HEAD_DIM,
                    "attn": rows * HEADS * HEAD_DIM, "proj": rows * HIDDEN, "mlp_gate": rows * INTER, "mlp_up": rows * INTER,
-                   "h_last": HIDDEN, "logits": 8 * VOCAB}
+                   "h_last": HIDDEN, "logits": 8 * VOCAB, "lin_qkv": rows * CONV_DIM, "lin_conv": rows * CONV_DIM,
+                   "lin_z": rows * VALUE_ALL, "lin_beta": rows * VALUE_HEADS, "lin_alpha": rows * VALUE_HEADS,
+                   "lin_core": rows * VALUE_ALL, "lin_out": rows * VALUE_ALL}
         for name, n in buffers.items():
             rt.alloc(name, n)
         for i in range(LAYERS):
-            rt.alloc(f"kc.{i}", KV_HEADS * HEAD_DIM * max_ctx)
-            rt.alloc(f"vc.{i}", KV_HEADS * HEAD_DIM * max_ctx)
+            if i in LINEAR_LAYERS:
+                rt.alloc(f"conv.{i}", CONV_DIM * CONV_K)
+                rt.alloc(f"ssm.{i}", VALUE_HEADS * KEY_DIM * VALUE_DIM)
+            else:
+                rt.alloc(f"kc.{i}", KV_HEADS * HEAD_DIM * max_ctx)
+                rt.alloc(f"vc.{i}", KV_HEADS * HEAD_DIM * max_ctx)
+
+    def linear_tail(self, i, n):
+        """What follows the four projections of a linear-attention layer, up to its output projection."""
+        rt, p = self.rt, f"blk.{i}."
+        rt.conv_update("lin_qkv", f"conv.{i}", p + "ssm_conv1d.weight", "lin_conv", CONV_DIM, CONV_K, n)
+        rt.gated_delta("lin_conv", "lin_beta", "lin_alpha", p + "ssm_a", p + "ssm_dt.bias", f"ssm.{i}", "lin_core", KEY_HEADS, VALUE_HEADS,
+                       KEY_DIM, VALUE_DIM, EPS, 0, n)
+        rt.gated_rmsnorm("lin_core", p + "ssm_norm.weight", "lin_z", "lin_out", VALUE_DIM, EPS, VALUE_HEADS * n)
 
     def forward(self, tokens):
         rt, n, pos = self.rt, len(tokens), self.position
@@ -117,18 +152,26 @@ class Driver:
         for i in range(LAYERS):
             p, kc, vc = f"blk.{i}.", f"kc.{i}", f"vc.{i}"
             rt.rmsnorm("h", p + "attn_norm.weight", "xn", HIDDEN, EPS, n)
-            rt.qmv(p + "attn_q.weight", "xn", "q_raw", n)
-            rt.qmv(p + "attn_k.weight", "xn", "k", n)
-            rt.qmv(p + "attn_v.weight", "xn", "v", n)
-            rt.split_gated_q("q_raw", "q", "q_gate", HEADS * n, HEAD_DIM)
-            rt.rmsnorm("q", p + "attn_q_norm.weight", "q", HEAD_DIM, EPS, HEADS * n)
-            rt.rmsnorm("k", p + "attn_k_norm.weight", "k", HEAD_DIM, EPS, KV_HEADS * n)
-            rt.rope("q", HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
-            rt.rope("k", KV_HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
-            rt.kv_append("k", "v", kc, vc, KV_HEADS, self.max_ctx, HEAD_DIM, pos, n)
-            rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, self.max_ctx, pos + 1, n)
-            rt.sigmoid_mul("attn", "q_gate", "attn", HEADS * HEAD_DIM * n)
-            rt.qmv(p + "attn_output.weight", "attn", "proj", n)
+            if i in LINEAR_LAYERS:
+                rt.qmv(p + "attn_qkv.weight", "xn", "lin_qkv", n)
+                rt.qmv(p + "attn_gate.weight", "xn", "lin_z", n)
+                rt.qmv(p + "ssm_beta.weight", "xn", "lin_beta", n)
+                rt.qmv(p + "ssm_alpha.weight", "xn", "lin_alpha", n)
+                self.linear_tail(i, n)
+                rt.qmv(p + "ssm_out.weight", "lin_out", "proj", n)
+            else:
+                rt.qmv(p + "attn_q.weight", "xn", "q_raw", n)
+                rt.qmv(p + "attn_k.weight", "xn", "k", n)
+                rt.qmv(p + "attn_v.weight", "xn", "v", n)
+                rt.split_gated_q("q_raw", "q", "q_gate", HEADS * n, HEAD_DIM)
+                rt.rmsnorm("q", p + "attn_q_norm.weight", "q", HEAD_DIM, EPS, HEADS * n)
+                rt.rmsnorm("k", p + "attn_k_norm.weight", "k", HEAD_DIM, EPS, KV_HEADS * n)
+                rt.rope("q", HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
+                rt.rope("k", KV_HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
+                rt.kv_append("k", "v", kc, vc, KV_HEADS, self.max_ctx, HEAD_DIM, pos, n)
+                rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, self.max_ctx, pos + 1, n)
+                rt.sigmoid_mul("attn", "q_gate", "attn", HEADS * HEAD_DIM * n)
+                rt.qmv(p + "attn_output.weight", "attn", "proj", n)
             rt.add("h", "proj", "h", HIDDEN * n)
             rt.rmsnorm("h", p + "post_attention_norm.weight", "xn", HIDDEN, EPS, n)
             rt.qmv(p + "ffn_gate.weight", "xn", "mlp_gate", n)
@@ -166,18 +209,24 @@ class FusedDriver(Driver):
         rt.write("h", np.ascontiguousarray(self.embeddings[tokens]).tobytes())
         for i in range(LAYERS):
             p, kc, vc = f"blk.{i}.", f"kc.{i}", f"vc.{i}"
-            rt.qmv_fused(p + "attn_q.weight", "h", "q_raw", n, norm=p + "attn_norm.weight")
-            rt.qmv_fused(p + "attn_k.weight", "h", "k", n, norm=p + "attn_norm.weight")
-            rt.qmv_fused(p + "attn_v.weight", "h", "v", n, norm=p + "attn_norm.weight")
-            rt.split_gated_q("q_raw", "q", "q_gate", HEADS * n, HEAD_DIM)
-            rt.rmsnorm("q", p + "attn_q_norm.weight", "q", HEAD_DIM, EPS, HEADS * n)
-            rt.rmsnorm("k", p + "attn_k_norm.weight", "k", HEAD_DIM, EPS, KV_HEADS * n)
-            rt.rope("q", HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
-            rt.rope("k", KV_HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
-            rt.kv_append("k", "v", kc, vc, KV_HEADS, self.max_ctx, HEAD_DIM, pos, n)
-            rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, self.max_ctx, pos + 1, n)
-            rt.sigmoid_mul("attn", "q_gate", "attn", HEADS * HEAD_DIM * n)
-            rt.qmv_fused(p + "attn_output.weight", "attn", "h", n, add=True)
+            if i in LINEAR_LAYERS:
+                for weight, out in (("attn_qkv", "lin_qkv"), ("attn_gate", "lin_z"), ("ssm_beta", "lin_beta"), ("ssm_alpha", "lin_alpha")):
+                    rt.qmv_fused(p + weight + ".weight", "h", out, n, norm=p + "attn_norm.weight")
+                self.linear_tail(i, n)
+                rt.qmv_fused(p + "ssm_out.weight", "lin_out", "h", n, add=True)
+            else:
+                rt.qmv_fused(p + "attn_q.weight", "h", "q_raw", n, norm=p + "attn_norm.weight")
+                rt.qmv_fused(p + "attn_k.weight", "h", "k", n, norm=p + "attn_norm.weight")
+                rt.qmv_fused(p + "attn_v.weight", "h", "v", n, norm=p + "attn_norm.weight")
+                rt.split_gated_q("q_raw", "q", "q_gate", HEADS * n, HEAD_DIM)
+                rt.rmsnorm("q", p + "attn_q_norm.weight", "q", HEAD_DIM, EPS, HEADS * n)
+                rt.rmsnorm("k", p + "attn_k_norm.weight", "k", HEAD_DIM, EPS, KV_HEADS * n)
+                rt.rope("q", HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
+                rt.rope("k", KV_HEADS, HEAD_DIM, ROTARY, pos, FREQ_BASE, n)
+                rt.kv_append("k", "v", kc, vc, KV_HEADS, self.max_ctx, HEAD_DIM, pos, n)
+                rt.attention("q", kc, vc, "attn", HEADS, KV_HEADS, HEAD_DIM, self.max_ctx, pos + 1, n)
+                rt.sigmoid_mul("attn", "q_gate", "attn", HEADS * HEAD_DIM * n)
+                rt.qmv_fused(p + "attn_output.weight", "attn", "h", n, add=True)
             rt.qmv_fused(p + "ffn_gate.weight", "h", "mlp_gate", n, norm=p + "post_attention_norm.weight")
             rt.qmv_fused(p + "ffn_up.weight", "h", "mlp_up", n, norm=p + "post_attention_norm.weight")
             rt.qmv_fused(p + "ffn_down.weight", "mlp_gate", "h", n, silu_mul="mlp_up", add=True)
@@ -198,7 +247,9 @@ def decode(driver, prompt, steps):
     ids, gap = [], np.inf
     for _ in range(steps):
         nxt = driver.greedy_next()
-        top = np.sort(driver.logits(1)[0])[-2:]
+        row = driver.logits(1)[0]
+        assert np.all(np.isfinite(row))
+        top = np.sort(row)[-2:]
         gap = min(gap, float(top[1] - top[0]))
         ids.append(int(nxt))
         driver.forward([nxt])
@@ -228,8 +279,8 @@ def test_greedy_tokens_are_the_same_with_the_matvecs_routed_to_this_library(code
         try:
             proxy = ProxyRuntime(mod.Runtime(codebooks["iq3s_grid"]), mine)
             got_ids, got_rows, _ = decode(Driver(proxy, tensors, embeddings), prompt, 20)
-            # 22 passes (prompt, 20 tokens, verification) of 7 matvecs per layer, 20 + 1 LM heads: all of them ran here
-            assert proxy.matvecs_here == 22 * 7 * LAYERS + 21
+            # 22 passes (prompt, 20 tokens, verification) of 7 or 8 matvecs per layer, 20 + 1 LM heads: all of them ran here
+            assert proxy.matvecs_here == 22 * MATVECS_PER_PASS + 21
         finally:
             mine.close()
         assert got_ids == want_ids
@@ -238,7 +289,7 @@ def test_greedy_tokens_are_the_same_with_the_matvecs_routed_to_this_library(code
         try:
             proxy = ProxyRuntime(mod.Runtime(codebooks["iq3s_grid"]), mine)
             fused_ids, fused_rows, _ = decode(FusedDriver(proxy, tensors, embeddings), prompt, 20)
-            assert proxy.matvecs_here == 22 * 7 * LAYERS + 21
+            assert proxy.matvecs_here == 22 * MATVECS_PER_PASS + 21
         finally:
             mine.close()
         assert fused_ids == want_ids
