@@ -15,10 +15,11 @@
 //     decoders never wait for global memory (F16 and F32, whose 256 columns are too wide for the ring, are decoded
 //     straight from global memory);
 //   * K is walked in stages of 64 (two to four stage buffers, as many as fit), each weight stage filled and consumed as
-//     two halves of 32 (the pipeline's slots): warps 0-15 dequantise the weight half-tile (four threads per row, one
-//     chunk of 8 weights each) with the exact block decoders - Q4_K, Q5_K, Q6_K, Q3_K and Q8_0 with a per-block header
-//     and constant shifts, see FastHeader - store it as fp16 in the K-major 128-byte-swizzled layout the tensor core reads,
-//     make the writes visible to the async proxy and arrive, once per warp, on the slot's "full" mbarrier;
+//     two halves of 32 (the pipeline's slots): warps 0-15 dequantise the weight half-tiles - warps 0-7 the first half
+//     of every stage, warps 8-15 the second; four threads per row, one chunk of 8 weights each, two rows per thread -
+//     with the exact block decoders (Q4_K, Q5_K, Q6_K, Q3_K and Q8_0 with a per-block header and constant shifts, see
+//     FastHeader), store them as fp16 in the K-major 128-byte-swizzled layout the tensor core reads, make the writes
+//     visible to the async proxy and arrive, once per warp, on the slot's "full" mbarrier;
 //   * one thread of warp 16 feeds the activations: per stage one TMA tile copy (cp.async.bulk.tensor.2d, 64 columns x
 //     the block's activation rows of an accumulator, written by the hardware in the same 128-byte swizzle; no
 //     multicast) that completes on the stage's own mbarrier; a stage is refilled once the MMAs of its second half are done;
@@ -427,14 +428,15 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTSlots; ++s) {
-            // one arrive per decoder warp, and in the first block of a pair one more for the second block's slot
-            bar_init(s32(&s_full[s]), kAThreads / 32 + ((PAIR && rank == 0) ? 1 : 0));
+            // one arrive per decoder warp of the group that owns the slot, and in the first block of a pair one more for the
+            // second block's slot
+            bar_init(s32(&s_full[s]), kAThreads / 64 + ((PAIR && rank == 0) ? 1 : 0));
             bar_init(s32(&s_empty[s]), 1);
         }
         for (int s = 0; s < kTStages; ++s) bar_init(s32(&s_xfull[s]), 1);  // the feeding thread's arrive with the stage's byte count
         bar_init(s32(&s_done), 1);
         for (int b = 0; b < 2; ++b) {
-            bar_init(s32(&s_raw_full[b]), kTM);         // one arrive (with its byte count) per first thread of a row
+            bar_init(s32(&s_raw_full[b]), kTM / 2);     // one arrive (with its byte count) per copy-issuing thread
             bar_init(s32(&s_raw_empty[b]), kAThreads / 32);  // every decoder warp is done with the buffer
         }
         s_failed = 0;
@@ -475,26 +477,35 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const __grid_co
 #endif
     if (warp < 16) {
         // ---- weight half-tile: four threads per row, one chunk each; chunk c of the stage (8 weights, 16 bytes of fp16)
-        //      goes to 16-byte slot c ^ (row % 8) of the row
-        //      (the four threads of a row are neighbours in a warp: their global loads fall into the same sectors)
-        // rows r + 128 * mr of the block; the rows of a warp go 0, 4, 1, 5, ...: the 8 lanes the store unit serves together
-        // then hit 8 different 16-byte columns of the swizzle (rows r and r + 4 use opposite halves)
+        //      goes to 16-byte slot c ^ (row % 8) of the row.
+        // What a warp does for a slot is one chain of dependent steps (wait for "empty", load, decode, store, proxy fence,
+        // arrive), so the warps are split into two groups that take the slots in turn - warps 0-7 the first K half of
+        // every stage, warps 8-15 the second - and a thread decodes two rows (r and r + 64) of each row half instead of
+        // one: twice the independent work per chain, half as many chains per warp (measured on one GPU with the TMA-fed
+        // activation tiles, 17408 x 5120 x 512: IQ4_XS with the generic decoder 103-105 instead of 108-113 us, the types
+        // with a fast decoder unchanged within the spread between runs).
+        // The rows of a warp go 0, 4, 1, 5, ...: the 8 lanes the store unit serves together then hit 8 different 16-byte
+        // columns of the swizzle (rows r and r + 4 use opposite halves).
+        constexpr int NR = 2 * MR;  // rows per thread: i -> row half i / 2, row r + 64 * (i % 2) of it
+        const int grp = warp >> 3;
         const int quarter = threadIdx.x & 3, r8 = (threadIdx.x >> 2) & 7;
-        const int r = (threadIdx.x >> 5) * 8 + ((r8 >> 1) | ((r8 & 1) << 2));
-        bool valid[MR];
-        const uint8_t *w_row[MR];
+        const int r = (warp & 7) * 8 + ((r8 >> 1) | ((r8 & 1) << 2));
+        bool valid[NR];
+        const uint8_t *w_row[NR];
 #pragma unroll
-        for (int mr = 0; mr < MR; ++mr) {
-            valid[mr] = row0 + mr * kRowsPerAcc + r < rows;
-            w_row[mr] = w + static_cast<size_t>(valid[mr] ? row0 + mr * kRowsPerAcc + r : 0) * row_bytes;
+        for (int i = 0; i < NR; ++i) {
+            const int row = row0 + (i >> 1) * kRowsPerAcc + r + 64 * (i & 1);
+            valid[i] = row < rows;
+            w_row[i] = w + static_cast<size_t>(valid[i] ? row : 0) * row_bytes;
         }
         // One slot of this thread: wait until the MMAs that read the slot's previous contents are done, store the 8 fp16
         // weights of chunk `quarter` of the half stage for each of its rows (swizzled), make them visible to the tensor
         // core, arrive.
         auto slot_wait = [&](int q) -> bool { return warp_wait(s32(&s_empty[q % kTSlots]), ((q / kTSlots) & 1) ^ 1, failed); };
-        auto slot_put = [&](int q, int mr, const uint32_t (&h)[4]) {
+        auto slot_put = [&](int q, int i, const uint32_t (&h)[4]) {
             const int slot = q % kTSlots, c = (slot & 1) * 4 + quarter;  // chunk within the stage
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tiles + (slot >> 1) * kTStage + (mr * kTM + r) * 128 + ((c ^ (r & 7)) << 4)),
+            const int row = (i >> 1) * kTM + r + 64 * (i & 1);          // row of the block's weight tile
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tiles + (slot >> 1) * kTStage + row * 128 + ((c ^ (r & 7)) << 4)),
                          "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3])
                          : "memory");
         };
@@ -513,26 +524,29 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const __grid_co
         };
         if constexpr (!kStaged) {
             static_assert(kStaged || MR == 1, "two row halves only with the raw ring");
-            for (int q = 0; q < n_slots; ++q) {
+            for (int q = grp; q < n_slots; q += 2) {
                 if (!slot_wait(q)) break;
                 const int kc = (q >> 1) * (kTK / 8) + (q & 1) * 4 + quarter;  // chunk within the row
-                uint32_t h[4] = {0u, 0u, 0u, 0u};
-                if (valid[0]) {
-                    float v[8];
-                    deq8<TYPE>(w_row[0] + static_cast<size_t>(kc / CPB) * BB, kc % CPB, v, table);
-                    to_f16(v, h);
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    uint32_t h[4] = {0u, 0u, 0u, 0u};
+                    if (valid[i]) {
+                        float v[8];
+                        deq8<TYPE>(w_row[i] + static_cast<size_t>(kc / CPB) * BB, kc % CPB, v, table);
+                        to_f16(v, h);
+                    }
+                    slot_put(q, i, h);
                 }
-                slot_put(q, 0, h);
                 slot_done(q);
             }
         } else {
-            // Raw ring: column `col` (256 weight columns) of this thread's rows goes to buffer col % 2.  The first thread of a
-            // row issues the copies of its rows; the bytes keep their position inside their 16-byte line.
+            // Raw ring: column `col` (256 weight columns) of the block's rows goes to buffer col % 2.  The first thread of a
+            // row in the first group issues the copies of its rows; the bytes keep their position inside their 16-byte line.
             constexpr int kSlotsPerCol = 2 * kRawCols / kTK;  // 8
             const int n_raw = (cols + kRawCols - 1) / kRawCols;
-            int raw_issued = 0;  // columns this thread has queued copies for (first thread of a row only)
+            int raw_issued = 0;  // columns this thread has queued copies for
             int raw_taken = 0;   // columns whose bytes this thread has waited for
-            auto issue_raw = [&](int col) -> bool {  // the whole warp calls it; true unless a wait gave up
+            auto issue_raw = [&](int col) -> bool {  // the whole warp calls it (first group only); true unless a wait gave up
                 const int b = col & 1;
                 if (col >= 2 && !warp_wait(s32(&s_raw_empty[b]), ((col >> 1) - 1) & 1, failed)) return false;
                 if (quarter == 0) {
@@ -540,81 +554,81 @@ __global__ void __launch_bounds__(kTThreads, 1) qgemm_tc5_kernel(const __grid_co
                     const long long at = static_cast<long long>(col) * RUN;
                     const uint32_t run = row_bytes - at < RUN ? static_cast<uint32_t>(row_bytes - at) : static_cast<uint32_t>(RUN);
                     const uint32_t bar = s32(&s_raw_full[b]);
-                    uintptr_t p[MR];
-                    uint32_t bytes[MR], total = 0;
+                    uintptr_t p[NR];
+                    uint32_t bytes[NR], total = 0;
 #pragma unroll
-                    for (int mr = 0; mr < MR; ++mr) {
-                        p[mr] = reinterpret_cast<uintptr_t>(w_row[mr]) + static_cast<uintptr_t>(at);
-                        bytes[mr] = valid[mr] ? ((static_cast<uint32_t>(p[mr]) & 15u) + run + 15u) & ~15u : 0u;
-                        total += bytes[mr];
+                    for (int i = 0; i < NR; ++i) {
+                        p[i] = reinterpret_cast<uintptr_t>(w_row[i]) + static_cast<uintptr_t>(at);
+                        bytes[i] = valid[i] ? ((static_cast<uint32_t>(p[i]) & 15u) + run + 15u) & ~15u : 0u;
+                        total += bytes[i];
                     }
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(total) : "memory");
 #pragma unroll
-                    for (int mr = 0; mr < MR; ++mr)
-                        if (bytes[mr])
+                    for (int i = 0; i < NR; ++i)
+                        if (bytes[i])
                             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                             raw_ring + ((b * MR + mr) * kTM + r) * RSLOT),
-                                         "l"(p[mr] & ~static_cast<uintptr_t>(15)), "r"(bytes[mr]), "r"(bar)
+                                             raw_ring + ((b * MR + (i >> 1)) * kTM + r + 64 * (i & 1)) * RSLOT),
+                                         "l"(p[i] & ~static_cast<uintptr_t>(15)), "r"(bytes[i]), "r"(bar)
                                          : "memory");
                 }
                 return true;
             };
-            // Before slot g of column col.  Column col + 1 goes into the buffer column col - 1 left two slots earlier: by then
-            // every decoder thread has normally handed it back, so the wait inside does not hold the row's first thread up.
+            // Before slot g of column col.  Column col + 1 goes into the buffer column col - 1 left a little earlier: by the
+            // first group's second slot every decoder warp has normally handed it back, so the wait inside holds nobody up.
             auto slot_begin = [&](int col, int g) -> bool {
                 if (g == 2 && col >= 1 && col + 1 < n_raw && !issue_raw(col + 1)) return false;
                 return slot_wait(col * kSlotsPerCol + g);
             };
-            bool alive = issue_raw(0) && (n_raw < 2 || issue_raw(1));
+            bool alive = grp != 0 || (issue_raw(0) && (n_raw < 2 || issue_raw(1)));
             for (int col = 0; alive && col < n_raw; ++col) {
                 if (!warp_wait(s32(&s_raw_full[col & 1]), (col >> 1) & 1, failed)) break;  // every lane: it reads the bytes
                 raw_taken = col + 1;
-                uint32_t blk[MR];  // the rows' blocks of this column
+                uint32_t blk[NR];  // the rows' blocks of this column
 #pragma unroll
-                for (int mr = 0; mr < MR; ++mr)
-                    blk[mr] = raw_ring + (((col & 1) * MR + mr) * kTM + r) * RSLOT +
-                              (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(w_row[mr]) + static_cast<uintptr_t>(col) * RUN) & 15u);
+                for (int i = 0; i < NR; ++i)
+                    blk[i] = raw_ring + (((col & 1) * MR + (i >> 1)) * kTM + r + 64 * (i & 1)) * RSLOT +
+                             (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(w_row[i]) + static_cast<uintptr_t>(col) * RUN) & 15u);
                 if constexpr (has_fast_chunk(TYPE)) {
-                    // one block per column; the block header is unpacked once, the eight slots are unrolled so that every
-                    // shift and byte position is a constant
-                    FastHeader<TYPE> hdr[MR];
+                    // one block per column; the block header is unpacked once, the group's four slots are unrolled so that
+                    // every shift and byte position is a constant
+                    FastHeader<TYPE> hdr[NR];
 #pragma unroll
-                    for (int mr = 0; mr < MR; ++mr) hdr[mr].load(blk[mr], quarter);
+                    for (int i = 0; i < NR; ++i) hdr[i].load(blk[i], quarter);
                     auto one = [&](auto g_tag) -> bool {
                         constexpr int G = decltype(g_tag)::value;
                         if (col * kSlotsPerCol + G >= n_slots) return true;  // the last run of a 32-weight-block type may be short
                         if (!slot_begin(col, G)) return false;
 #pragma unroll
-                        for (int mr = 0; mr < MR; ++mr) {
+                        for (int i = 0; i < NR; ++i) {
                             uint32_t h[4] = {0u, 0u, 0u, 0u};
 #if !(VQM_TC5_ABLATE & 1)
-                            if (valid[mr]) hdr[mr].template chunk<G>(blk[mr], quarter, h);
+                            if (valid[i]) hdr[i].template chunk<G>(blk[i], quarter, h);
 #endif
-                            slot_put(col * kSlotsPerCol + G, mr, h);
+                            slot_put(col * kSlotsPerCol + G, i, h);
                         }
                         slot_done(col * kSlotsPerCol + G);
                         return true;
                     };
-                    alive = one(Int<0>{}) && one(Int<1>{}) && one(Int<2>{}) && one(Int<3>{}) && one(Int<4>{}) && one(Int<5>{}) && one(Int<6>{}) &&
-                            one(Int<7>{});
+                    if (grp == 0) alive = one(Int<0>{}) && one(Int<2>{}) && one(Int<4>{}) && one(Int<6>{});
+                    else alive = one(Int<1>{}) && one(Int<3>{}) && one(Int<5>{}) && one(Int<7>{});
                 } else {
                     const int slots_here = n_slots - col * kSlotsPerCol < kSlotsPerCol ? n_slots - col * kSlotsPerCol : kSlotsPerCol;
 #pragma unroll 1
-                    for (int g = 0; g < slots_here; ++g) {
+                    for (int g = grp; g < slots_here; g += 2) {
                         if (!slot_begin(col, g)) {
                             alive = false;
                             break;
                         }
                         const int in_col = g * 4 + quarter;  // chunk within the column
 #pragma unroll
-                        for (int mr = 0; mr < MR; ++mr) {
+                        for (int i = 0; i < NR; ++i) {
                             uint32_t h[4] = {0u, 0u, 0u, 0u};
-                            if (valid[mr]) {
+                            if (valid[i]) {
                                 float v[8];
-                                deq8<TYPE>(static_cast<const uint8_t *>(__cvta_shared_to_generic(blk[mr] + (in_col / CPB) * BB)), in_col % CPB, v, table);
+                                deq8<TYPE>(static_cast<const uint8_t *>(__cvta_shared_to_generic(blk[i] + (in_col / CPB) * BB)), in_col % CPB, v, table);
                                 to_f16(v, h);
                             }
-                            slot_put(col * kSlotsPerCol + g, mr, h);
+                            slot_put(col * kSlotsPerCol + g, i, h);
                         }
                         slot_done(col * kSlotsPerCol + g);
                     }
