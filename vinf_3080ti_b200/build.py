@@ -4,8 +4,10 @@
 
 --define passes -DNAME[=VALUE] to every translation unit: the kernels' experiment switches (VQM_ABLATE_STEP: the matvec
 pipeline without the decoders; VQM_PURE_COMPUTE: the decoders without copies and waits; VQM_NO_SCALE_PASS / VQM_NO_DOT:
-without one of the two passes of the tuned K-quant decoders) give the ablation timings quoted in profiles/.  Such a build
-goes to --out (objects beside it) and is loaded with VINF_B200_LIB=<path>; its results are wrong on purpose.
+without one of the two passes of the tuned K-quant decoders; VQM_TC5_ABLATE=<bits>: the prompt GEMM without decode /
+activation copies / proxy fence / everything but the MMA loop) give the ablation timings quoted in profiles/; their
+results are wrong on purpose.  VQM_TC5_SHAPE=<n> selects another block shape of the prompt GEMM (results stay right).
+Such a build goes to --out (objects beside it) and is loaded with VINF_B200_LIB=<path>.
 
 Two translation units per GGUF type (the matvec kernel instantiations, plain and with the fused prologues) plus the small kernels and the
 runtime; objects go to csrc/build/, the library next to this file.  Cross-compiles without a GPU.
