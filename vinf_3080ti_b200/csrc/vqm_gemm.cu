@@ -8,8 +8,8 @@
 // rounded to fp16, products are exact, sums are fp32), and every output is a dot product in the same K order
 // whatever the tiling.  Two shared-memory stages overlap the next tile's decode and copies with the MMAs.
 //
-// This is the warp-level tensor-core path (below tcgen05 throughput).  Passes of 128 activation rows or more take the
-// tcgen05 kernel in vqm_gemm_tc5.cu; this one serves 64..127 rows and column counts that are not multiples of 64.  It is
+// This is the warp-level tensor-core path (below tcgen05 throughput).  Passes of 64 activation rows or more take the
+// tcgen05 kernel in vqm_gemm_tc5.cu; this one serves fewer rows and column counts that are not multiples of 64.  It is
 // only used when the caller asks for it (set_gemm_min_rows), as in the reference; decode and verification passes always
 // take the fp32 matvec.
 #include <cuda_fp16.h>

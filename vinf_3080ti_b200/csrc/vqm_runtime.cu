@@ -782,8 +782,8 @@ int vqm_qmv(vqm_runtime *rt, const char *weight, const char *x, const char *y, i
         const uint8_t *cb = codebook_for(rt, t->type);
         if (vqm::grid_is_codebook(t->type) && cb == nullptr)
             return fail(VQM_ERR_VALUE, "the codebook for GGUF type %d has not been set (vqm_set_codebook)", t->type);
-        // tcgen05 kernel (activation buffer padded to 512 rows) from 128 rows on, the warp-level MMA kernel below that
-        const bool tc5 = rt->gemm_tcgen05 && ntok >= 128 && vqm::gemm_tc5_supports(t->cols);
+        // tcgen05 kernel (activation buffer padded to 512 rows) from 64 rows on, the warp-level MMA kernel below that
+        const bool tc5 = rt->gemm_tcgen05 && ntok >= 64 && vqm::gemm_tc5_supports(t->cols);
         const int tile = tc5 ? vqm::gemm_tc5_token_tile() : vqm::gemm_token_tile();
         const size_t need = static_cast<size_t>((ntok + tile - 1) / tile * tile) * t->cols;
         cudaError_t err = cudaSuccess;
